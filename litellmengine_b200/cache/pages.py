@@ -92,7 +92,8 @@ class PagePool:
 class PagedNeed:
     """What a stage asks of the cache when it keeps keys and values by position: per position,
     `num_kv_heads` keys of `head_dim` values and as many values of `value_dim` (None: of
-    `head_dim` too, and keys and values then share one tensor with an axis of two)."""
+    `head_dim` too, and keys and values then share one tensor with an axis of two; 0: keys only, for a stage
+    whose values are a part of its key rows)."""
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None      # None: every earlier position stays; w: only the last w
@@ -109,9 +110,12 @@ class PagedNeed:
 
 @dataclass(frozen=True)
 class StateNeed:
-    """What a stage asks when it keeps a state of fixed size per request (zeroed at admission)."""
+    """What a stage asks when it keeps a state of fixed size per request (zeroed at admission).  `name` '' is the
+    mixer's own state (`CacheManager.state[stage]`); a named one belongs to another part of the layer
+    (`CacheManager.state[(stage, name)]`), so a stage can keep one of each name."""
     shape: Tuple[int, ...]
     dtype: str = "float32"
+    name: str = ""
 
 
 class CacheGroup:
@@ -187,7 +191,7 @@ class CacheManager:
 
         self.groups: List[CacheGroup] = []
         self.stage_group: Dict[int, Tuple[int, int]] = {}     # stage -> (group index, index inside group)
-        self.stage_state: Dict[int, StateNeed] = {}
+        self.stage_state: Dict[object, StateNeed] = {}          # stage, or (stage, name) for a named state
         by_need: Dict[PagedNeed, int] = {}
         for s, need in ((s, n) for s, ns in enumerate(stage_needs) for n in ns):
             if isinstance(need, PagedNeed):
@@ -202,9 +206,10 @@ class CacheManager:
                 self.stage_group[s] = (gi, len(g.stages))
                 g.stages.append(s)
             elif isinstance(need, StateNeed):
-                if s in self.stage_state:
+                key = (s, need.name) if need.name else s
+                if key in self.stage_state:
                     raise CacheError(f"stage {s} asks for a state twice")
-                self.stage_state[s] = need
+                self.stage_state[key] = need
         for s, need in ((s, n) for s, ns in enumerate(stage_needs) for n in ns):
             if isinstance(need, tuple) and need and need[0] == "borrow":
                 src = need[1]

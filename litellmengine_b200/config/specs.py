@@ -75,6 +75,17 @@ class MixerSpec:
     running maximum per head (`params`: gate_cap, eps).
     `tensor_names` renames a mixer's tensors: pairs (the mixer's own name for a tensor, its name in the
     model's files, without the mixer's prefix).
+    `head_temperature`: a learned number per query head (tensor 'temp' [heads]) multiplies the scaled score.
+    `log_distance_bias`: r1[h] * ln(1 + r2[h] * (i - j)) is taken off the score of query i and key j, with two
+    learned numbers per query head (tensors 'r1', 'r2' [heads]); unlike `distance_bias` it has no farthest row.
+    kind 'latent_attention': softmax attention whose keys and values are made from a cached latent: queries
+    through a normed low-rank latent (`params`: q_rank), per token one normed latent of `params` kv_rank entries
+    and one rotated key part of `params` rot_dim entries shared by all heads go to the pages; per head the
+    unrotated key (`head_dim` entries) and the value (`value_dim`) are linear maps of the latent; `position`
+    rotates the rot_dim part of queries and keys; `window`, `scale`, `output_gate` as for attention; `params`
+    eps (of the two latent norms), keep_window (the pages keep so many positions: the widest window among the
+    stages that read them; None: all).  With `has_kv` False the mixer has no latent projection of its own and
+    reads the pages of the stage named by `cache_from`.
     """
     kind: str
     num_heads: int = 0
@@ -97,11 +108,14 @@ class MixerSpec:
     tensor_names: Tuple[Tuple[str, str], ...] = ()
     output_gate_scope: str = "channel"
     distance_bias: Optional[Tuple[int, float]] = None
+    head_temperature: bool = False
+    log_distance_bias: bool = False
 
 
 @dataclass(frozen=True)
 class FeedForwardSpec:
-    """The per-token part of a layer.  kind 'swiglu': down(silu(gate(x)) * up(x)).
+    """The per-token part of a layer.  kind 'swiglu': down(act(gate(x)) * up(x)) with act = silu, or what
+    `params` activation names ('silu', 'gelu_tanh': 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))).
     kind 'moe': routed experts; `intermediate_size` is one expert's, `params`: experts, top, groups
     (count, keep) or None, route_scale, limit (the experts' clamp), expert_prefix (expert e's tensors are
     '<expert_prefix><e>.gate' and so on).
@@ -122,6 +136,11 @@ class BlockSpec:
     outputs, and the sublayers read the stream itself.
     arrangement 'hyper_pre_norm': the pre-norm layer over `streams` copies of the residual stream (see
     `connections`).
+    arrangement 'post_norm': h <- norm1(residual_scale * h + mixer(u(h))); h <- norm2(residual_scale * h + ffn(u(h))):
+    the norm comes after the sum and the sublayers read the stream itself, or, with `input_conv` = taps, the stream
+    plus its causal convolution over time, channel by channel: u_t = h_t + sum_j w[:, j] * h_(t - taps + 1 + j) with
+    zeros before the sequence's start (tensors `input_conv_names`, one [hidden, taps] per sublayer; the last taps - 1
+    rows of h are kept per request, layer and sublayer).
     `feed_forward` None: a layer that is its mixer only.
     `connections` = (streams, name of the mixer's connection tensors, name of the feed-forward's): each
     sublayer has tensors `<name>.in` [streams], `<name>.out` [streams], `<name>.mix` [streams, streams]; its
@@ -136,6 +155,9 @@ class BlockSpec:
     mixer_norm_name: str = "input_layernorm"
     feed_forward_norm_name: str = "post_attention_layernorm"
     connections: Optional[Tuple[int, str, str]] = None
+    residual_scale: float = 1.0
+    input_conv: Optional[int] = None
+    input_conv_names: Tuple[str, str] = ("conv1", "conv2")
 
 
 @dataclass(frozen=True)

@@ -1,4 +1,5 @@
-// SwiGLU's elementwise middle: out[t, i] = silu(gu[t, i]) * gu[t, inter + i], silu(g) = g / (1 + exp(-g))
+// A gated feed-forward's elementwise middle: out[t, i] = act(gu[t, i]) * gu[t, inter + i] with act = silu,
+// silu(g) = g / (1 + exp(-g)), or (act_kind 1) the tanh form of gelu, 0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))),
 // in 32-bit (src/ops/silu_and_mul.cu:44-46,76-79).  The gate and up projections are one fused
 // matrix product, so both halves of a row sit side by side.
 // Also the plain residual add h += delta in 32-bit (src/ops/add.cu:16-27).
@@ -6,10 +7,14 @@
 #include <algorithm>
 
 __device__ __forceinline__ float silu(float g) { return g / (1.0f + expf(-g)); }
+__device__ __forceinline__ float gelu_tanh(float g) {
+    return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+}
+__device__ __forceinline__ float gate_act(float g, int kind) { return kind == 1 ? gelu_tanh(g) : silu(g); }
 
 // grid (blocks along the row, tokens): a thread takes 8 consecutive features of one token.
 template <typename T>
-__global__ void silu_and_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter) {
+__global__ void silu_and_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter, int act) {
     pdl_begin();
     const size_t t = blockIdx.y;
     const T* g = gu + t * 2 * inter;
@@ -22,19 +27,19 @@ __global__ void silu_and_mul_kernel(const T* __restrict__ gu, T* __restrict__ ou
             load8(g + i, a);
             load8(u + i, b);
 #pragma unroll
-            for (int k = 0; k < 8; ++k) r[k] = silu(a[k]) * b[k];
+            for (int k = 0; k < 8; ++k) r[k] = gate_act(a[k], act) * b[k];
             store8(o + i, r);
         }
     } else {
         for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < inter; i += gridDim.x * blockDim.x)
-            o[i] = from_f32<T>(silu(to_f32(g[i])) * to_f32(u[i]));
+            o[i] = from_f32<T>(gate_act(to_f32(g[i]), act) * to_f32(u[i]));
     }
 }
 
-extern "C" int llm_silu_and_mul(const void* gu, void* out, int dtype, int num_tokens, int inter,
+extern "C" int llm_silu_and_mul(const void* gu, void* out, int dtype, int num_tokens, int inter, int act,
                                 uintptr_t stream) {
     if (num_tokens <= 0) return LLM_OK;
-    if (inter <= 0 || num_tokens > 65535) return LLM_REFUSED_SIZE;
+    if (inter <= 0 || num_tokens > 65535 || act < 0 || act > 1) return LLM_REFUSED_SIZE;
     if ((inter & 7) == 0 && (!aligned16(gu) || !aligned16(out))) return LLM_REFUSED_ALIGN;
     const int threads = 256;
     const int per_row = (inter & 7) == 0 ? inter / 8 : inter;
@@ -42,10 +47,10 @@ extern "C" int llm_silu_and_mul(const void* gu, void* out, int dtype, int num_to
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     if (dtype == LLM_DT_F32)
         launch_pdl((silu_and_mul_kernel<float>), grid, dim3(threads), 0, s, static_cast<const float*>(gu),
-                   static_cast<float*>(out), inter);
+                   static_cast<float*>(out), inter, act);
     else if (dtype == LLM_DT_BF16)
         launch_pdl((silu_and_mul_kernel<bf16>), grid, dim3(threads), 0, s, static_cast<const bf16*>(gu),
-                   static_cast<bf16*>(out), inter);
+                   static_cast<bf16*>(out), inter, act);
     else
         return LLM_REFUSED_DTYPE;
     return launch_status();
@@ -56,7 +61,7 @@ extern "C" int llm_silu_and_mul(const void* gu, void* out, int dtype, int num_to
 // what reading the finished bfloat16 product would have given.
 template <typename T>
 __global__ void silu_and_mul_parts_kernel(const float* __restrict__ parts, int slices, T* __restrict__ out, int inter,
-                                          long long slice_stride) {
+                                          long long slice_stride, int act) {
     pdl_begin();
     const size_t t = blockIdx.y;
     const float* g = parts + t * 2 * inter;
@@ -67,22 +72,22 @@ __global__ void silu_and_mul_parts_kernel(const float* __restrict__ parts, int s
             a += g[z * slice_stride + i];
             b += g[z * slice_stride + inter + i];
         }
-        o[i] = from_f32<T>(silu(to_f32(from_f32<T>(a))) * to_f32(from_f32<T>(b)));
+        o[i] = from_f32<T>(gate_act(to_f32(from_f32<T>(a)), act) * to_f32(from_f32<T>(b)));
     }
 }
 
 extern "C" int llm_silu_and_mul_parts(const float* parts, int slices, void* out, int dtype, int num_tokens, int inter,
-                                      uintptr_t stream) {
+                                      int act, uintptr_t stream) {
     if (num_tokens <= 0) return LLM_OK;
-    if (inter <= 0 || num_tokens > 65535 || slices < 1) return LLM_REFUSED_SIZE;
+    if (inter <= 0 || num_tokens > 65535 || slices < 1 || act < 0 || act > 1) return LLM_REFUSED_SIZE;
     const int threads = 256;
     const dim3 grid(std::min((inter + threads - 1) / threads, 4096), num_tokens);
     const long long stride = static_cast<long long>(num_tokens) * 2 * inter;
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     if (dtype == LLM_DT_F32)
-        launch_pdl((silu_and_mul_parts_kernel<float>), grid, dim3(threads), 0, s, parts, slices, static_cast<float*>(out), inter, stride);
+        launch_pdl((silu_and_mul_parts_kernel<float>), grid, dim3(threads), 0, s, parts, slices, static_cast<float*>(out), inter, stride, act);
     else if (dtype == LLM_DT_BF16)
-        launch_pdl((silu_and_mul_parts_kernel<bf16>), grid, dim3(threads), 0, s, parts, slices, static_cast<bf16*>(out), inter, stride);
+        launch_pdl((silu_and_mul_parts_kernel<bf16>), grid, dim3(threads), 0, s, parts, slices, static_cast<bf16*>(out), inter, stride, act);
     else
         return LLM_REFUSED_DTYPE;
     return launch_status();

@@ -31,15 +31,22 @@
 // An optional learned bias by distance is added to the scaled score: s_j += dist_bias[min(p - j, len - 1),
 // h], a float32 table [len, heads] indexed by the distance itself (whoever owns the table expands its
 // bucketing into one row per distance up to the distance from which the row no longer changes).
+// An analytic one instead (`log_r1`, `log_r2`, float32 [heads]): s_j -= r1[h] * ln(1 + r2[h] * (p - j)), which has
+// no farthest row.  `head_scale` (float32 [heads]) multiplies a head's scaled scores (a learned temperature).
+// `value_row_stride` (elements; 0: dv) lets the values be the first dv entries of rows that are wider, e.g. of
+// the key rows themselves: a layer that caches one latent row per token, scores against all of it and sums its
+// first part needs no second tensor.  Value widths above 256 take an instantiation with twice the accumulators.
 // With `rows` (int32 [num_tokens]) the kernel works on the listed tokens only (a step's single decoded tokens
 // while its prompt portions take a tensor-core kernel); -1 entries pad the list.
 #include "common.cuh"
 #include <math_constants.h>
 
 #define AG_WARPS 8
-#define AG_MAX_D 256
+#define AG_MAX_D 256           // value width of the usual instantiation
+#define AG_MAX_DV 512          // and of the wide one
+#define AG_MAX_DK 1024         // key width (q is held in shared memory)
 
-template <typename T, typename TC>
+template <typename T, typename TC, int MAXDV>
 __global__ void paged_attention_generic_kernel(
     const T* __restrict__ q, T* __restrict__ out, const TC* __restrict__ keys, const TC* __restrict__ values,
     long long key_page_stride, long long value_page_stride,
@@ -48,7 +55,9 @@ __global__ void paged_attention_generic_kernel(
     int num_tokens, int nq, int nkv, int d, int dv, int page_size, int window, float scale, int num_pages,
     const float* __restrict__ gate, long long gate_stride, int gate_off, float out_scale,
     long long out_stride, int out_off, int vec, int32_t* __restrict__ status,
-    const float* __restrict__ dist_bias, int dist_len, int gate_per_head, const int32_t* __restrict__ rows) {
+    const float* __restrict__ dist_bias, int dist_len, int gate_per_head, const int32_t* __restrict__ rows,
+    const float* __restrict__ head_scale, const float* __restrict__ log_r1, const float* __restrict__ log_r2,
+    long long value_row_stride) {
     pdl_begin();
     extern __shared__ float smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -61,20 +70,23 @@ __global__ void paged_attention_generic_kernel(
     float* qs = smem;                                  // [d]
     float* merge = smem + d;                           // [AG_WARPS][dv + 2]: output, maximum, sum of each warp
     const T* qrow = q + (static_cast<size_t>(t) * nq + h) * d;
-    for (int i = threadIdx.x; i < d; i += AG_WARPS * 32) qs[i] = to_f32(qrow[i]) * scale;
+    const float hscale = head_scale ? scale * head_scale[h] : scale;
+    for (int i = threadIdx.x; i < d; i += AG_WARPS * 32) qs[i] = to_f32(qrow[i]) * hscale;
     __syncthreads();
+    const float r1 = log_r1 ? log_r1[h] : 0.0f, r2 = log_r1 ? log_r2[h] : 0.0f;
 
     const int pos = positions[t];
     const int slot = entry_slot[token_entry[t]];
     const int32_t* table = block_table + static_cast<size_t>(slot) * table_stride;
     const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
     const size_t khead = static_cast<size_t>(page_size) * d;        // one kv head inside a page of keys
-    const size_t vhead = static_cast<size_t>(page_size) * dv;       // and inside a page of values
+    const size_t vrow = value_row_stride > 0 ? static_cast<size_t>(value_row_stride) : static_cast<size_t>(dv);
+    const size_t vhead = static_cast<size_t>(page_size) * vrow;     // and inside a page of values
 
     float m = -CUDART_INF_F, l = 0.0f;
-    float acc[AG_MAX_D / 32];
+    float acc[MAXDV / 32];
 #pragma unroll
-    for (int r = 0; r < AG_MAX_D / 32; ++r) acc[r] = 0.0f;
+    for (int r = 0; r < MAXDV / 32; ++r) acc[r] = 0.0f;
 
     for (int base = lo + 32 * warp; base <= pos; base += 32 * AG_WARPS) {
         const int j = base + lane;
@@ -90,7 +102,7 @@ __global__ void paged_attention_generic_kernel(
                 const TC* kr = keys + static_cast<long long>(page) * key_page_stride + kvh * khead +
                                static_cast<size_t>(j % page_size) * d;
                 voff = static_cast<long long>(page) * value_page_stride + kvh * vhead +
-                       static_cast<size_t>(j % page_size) * dv;
+                       static_cast<size_t>(j % page_size) * vrow;
                 float dot = 0.0f;
                 if (vec) {
                     for (int i = 0; i < d; i += 8) {
@@ -104,6 +116,7 @@ __global__ void paged_attention_generic_kernel(
                 }
                 s = dot;
                 if (dist_bias) s += dist_bias[static_cast<size_t>(min(pos - j, dist_len - 1)) * nq + h];
+                if (log_r1) s -= r1 * log1pf(r2 * static_cast<float>(pos - j));
             }
         }
         const float m_new = fmaxf(m, warp_max(s));
@@ -112,7 +125,7 @@ __global__ void paged_attention_generic_kernel(
         l = l * alpha + warp_sum(p);
         m = m_new;
 #pragma unroll
-        for (int r = 0; r < AG_MAX_D / 32; ++r) acc[r] *= alpha;
+        for (int r = 0; r < MAXDV / 32; ++r) acc[r] *= alpha;
         const int count = min(32, pos - base + 1);
         const int regs = (dv + 31) >> 5;               // value entries a lane holds
         for (int jj = 0; jj < count; jj += 4) {       // four keys' value rows in flight: their loads do not wait for one another
@@ -126,9 +139,10 @@ __global__ void paged_attention_generic_kernel(
                 pj[u] = use ? pu : 0.0f;
                 vr[u] = values + (use ? vo : 0);
             }
-            for (int r = 0; r < regs; ++r) {
+#pragma unroll
+            for (int r = 0; r < MAXDV / 32; ++r) {
                 const int i = lane + 32 * r;
-                if (i < dv) {
+                if (r < regs && i < dv) {
                     float x[4];
 #pragma unroll
                     for (int u = 0; u < 4; ++u) x[u] = to_f32(vr[u][i]);
@@ -141,7 +155,7 @@ __global__ void paged_attention_generic_kernel(
     // merge the warps' partial results, in warp order (a warp without tiles has m = -inf, l = 0)
     float* mine = merge + warp * (dv + 2);
 #pragma unroll
-    for (int r = 0; r < AG_MAX_D / 32; ++r) {
+    for (int r = 0; r < MAXDV / 32; ++r) {
         const int i = lane + 32 * r;
         if (i < dv) mine[i] = acc[r];
     }
@@ -178,9 +192,12 @@ extern "C" int llm_paged_attention_generic_kv(
     const int32_t* token_entry, const int32_t* entry_slot, const int32_t* block_table, int table_stride,
     int num_tokens, int nq, int nkv, int d, int dv, int page_size, int window, float scale, int num_pages,
     const float* gate, long long gate_stride, int gate_off, float out_scale, long long out_stride, int out_off,
-    int32_t* status, const float* dist_bias, int dist_len, int gate_per_head, const int32_t* rows, uintptr_t stream) {
+    int32_t* status, const float* dist_bias, int dist_len, int gate_per_head, const int32_t* rows,
+    const float* head_scale, const float* log_r1, const float* log_r2, long long value_row_stride, uintptr_t stream) {
     if (num_tokens <= 0) return LLM_OK;
-    if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || d <= 0 || d > AG_MAX_D || dv <= 0 || dv > AG_MAX_D || page_size <= 0)
+    if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || d <= 0 || d > AG_MAX_DK || dv <= 0 || dv > AG_MAX_DV || page_size <= 0)
+        return LLM_REFUSED_SIZE;
+    if ((log_r1 == nullptr) != (log_r2 == nullptr) || value_row_stride < 0 || (value_row_stride > 0 && value_row_stride < dv))
         return LLM_REFUSED_SIZE;
     if (dist_bias && dist_len <= 0) return LLM_REFUSED_SIZE;
     const int esz = cache_dtype == LLM_DT_F32 ? 4 : 2;
@@ -191,18 +208,21 @@ extern "C" int llm_paged_attention_generic_kv(
     const unsigned blocks = static_cast<unsigned>(items);
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
 #define LAUNCH(T, TC)                                                                              \
-    launch_pdl((paged_attention_generic_kernel<T, TC>), dim3(blocks), dim3(AG_WARPS * 32), smem, s,                      \
+    if (dv > AG_MAX_D) LAUNCH_W(T, TC, AG_MAX_DV); else LAUNCH_W(T, TC, AG_MAX_D)
+#define LAUNCH_W(T, TC, W)                                                                         \
+    launch_pdl((paged_attention_generic_kernel<T, TC, W>), dim3(blocks), dim3(AG_WARPS * 32), smem, s,                      \
         static_cast<const T*>(q), static_cast<T*>(out), static_cast<const TC*>(keys),               \
         static_cast<const TC*>(values), key_page_stride, value_page_stride, positions,             \
         token_entry, entry_slot, block_table, table_stride, num_tokens, nq, nkv, d, dv, page_size, \
         window, scale, num_pages, gate, gate_stride, gate_off, out_scale, out_stride, out_off, vec, status, \
-        dist_bias, dist_len, gate_per_head, rows)
-    if (dtype == LLM_DT_F32 && cache_dtype == LLM_DT_F32) LAUNCH(float, float);
-    else if (dtype == LLM_DT_BF16 && cache_dtype == LLM_DT_BF16) LAUNCH(bf16, bf16);
-    else if (dtype == LLM_DT_F32 && cache_dtype == LLM_DT_BF16) LAUNCH(float, bf16);
-    else if (dtype == LLM_DT_BF16 && cache_dtype == LLM_DT_F32) LAUNCH(bf16, float);
+        dist_bias, dist_len, gate_per_head, rows, head_scale, log_r1, log_r2, value_row_stride)
+    if (dtype == LLM_DT_F32 && cache_dtype == LLM_DT_F32) { LAUNCH(float, float); }
+    else if (dtype == LLM_DT_BF16 && cache_dtype == LLM_DT_BF16) { LAUNCH(bf16, bf16); }
+    else if (dtype == LLM_DT_F32 && cache_dtype == LLM_DT_BF16) { LAUNCH(float, bf16); }
+    else if (dtype == LLM_DT_BF16 && cache_dtype == LLM_DT_F32) { LAUNCH(bf16, float); }
     else return LLM_REFUSED_DTYPE;
 #undef LAUNCH
+#undef LAUNCH_W
     return launch_status();
 }
 
@@ -222,5 +242,5 @@ extern "C" int llm_paged_attention_generic(
                                           cache_dtype, 2 * half, 2 * half, positions, token_entry, entry_slot,
                                           block_table, table_stride, num_tokens, nq, nkv, d, d, page_size, window,
                                           scale, num_pages, nullptr, 0, 0, 1.0f, static_cast<long long>(nq) * d, 0,
-                                          status, nullptr, 0, 0, nullptr, stream);
+                                          status, nullptr, 0, 0, nullptr, nullptr, nullptr, nullptr, 0, stream);
 }

@@ -33,6 +33,8 @@ FAMILIES: Dict[str, List[str]] = {
     "attention_prepare": ["attention_prepare.cu"],
     "linear_attention": ["linear_attention.cu"],
     "streams": ["streams.cu"],
+    "conv_norm": ["conv_norm.cu"],
+    "latent_attention": ["latent_attention.cu"],
     "moe": ["moe.cu"],
     "attention_decode": ["attention_decode.cu"],
     "attention_prefill": ["attention_prefill.cu"],

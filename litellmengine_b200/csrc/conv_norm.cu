@@ -1,0 +1,140 @@
+// The two kernels around a sublayer of a layer whose norm follows the sum and whose sublayers read the
+// residual stream through a short causal convolution over time:
+//
+//   short_conv        u[t, c] = x[t, c] + sum_j w[c, j] * x_(t - taps + 1 + j)[c]       (j = 0 .. taps - 1)
+//                     x is the float32 stream [T, W]; the rows of earlier tokens of the same request come from
+//                     the step's own rows when the token's portion holds them, else from the request's kept
+//                     rows, and are zero before the sequence's start; u is stored in the compute dtype (it
+//                     feeds matrix products).  The arithmetic is 32-bit.
+//   scaled_add_norm   x[t, :] <- rmsnorm(alpha * x[t, :] + y[t, :]) * w, in place, in 32-bit; y may be a product
+//                     left as its k-splits (added in order while reading).  On the way the kernel keeps the
+//                     OLD row x[t, :] (what the sublayer before this norm read through its convolution) for the
+//                     request's next step, if the token is among the last taps - 1 of its portion.
+//
+// Kept rows.  Per request slot and sublayer a ring of R = taps - 1 rows of W floats; the row of the token at
+// position p sits at ring row p mod R.  The convolution of a token at position p reads positions p - 1 .. p - R
+// (R different ring rows); the ring is written by the norm kernel, which runs after the convolution of the same
+// sublayer has read it, and only the last R tokens of a portion write (R different ring rows), so no row is
+// written twice in a step and none is read after it was overwritten.  A portion may be cut anywhere and be as
+// short as one token.
+#include "common.cuh"
+
+#define CN_THREADS 256
+
+template <typename TO, int V>
+__global__ void short_conv_kernel(
+    const float* __restrict__ x, const float* __restrict__ w, TO* __restrict__ out, const float* __restrict__ kept,
+    long long kept_slot_stride, const int32_t* __restrict__ positions, const int32_t* __restrict__ token_entry,
+    const int32_t* __restrict__ entry_slot, const int32_t* __restrict__ entry_q_start, int width, int taps) {
+    pdl_begin();
+    const int t = blockIdx.x;
+    const int c = (blockIdx.y * CN_THREADS + threadIdx.x) * V;
+    if (c >= width) return;
+    const int e = token_entry[t];
+    const int q0 = entry_q_start[e], pos = positions[t];
+    const int R = taps - 1;
+    const float* ring = kept ? kept + static_cast<size_t>(entry_slot[e]) * kept_slot_stride : nullptr;
+    float acc[V], cur[V];
+#pragma unroll
+    for (int u = 0; u < V; ++u) cur[u] = x[static_cast<size_t>(t) * width + c + u];
+#pragma unroll
+    for (int u = 0; u < V; ++u) acc[u] = cur[u];
+    for (int back = R; back >= 0; --back) {                 // oldest first: the order of additions is fixed
+        const int j = taps - 1 - back;
+        const float* src = nullptr;
+        if (back == 0) src = nullptr;
+        else if (t - back >= q0) src = x + static_cast<size_t>(t - back) * width + c;
+        else if (pos - back >= 0 && ring) src = ring + static_cast<size_t>((pos - back) % R) * width + c;
+        else continue;                                      // before the sequence's start: zero
+#pragma unroll
+        for (int u = 0; u < V; ++u) acc[u] += w[static_cast<size_t>(c + u) * taps + j] * (back == 0 ? cur[u] : src[u]);
+    }
+#pragma unroll
+    for (int u = 0; u < V; ++u) out[static_cast<size_t>(t) * width + c + u] = from_f32<TO>(acc[u]);
+}
+
+extern "C" int llm_short_conv(const float* x, const float* w, void* out, int out_dtype, const float* kept,
+                              long long kept_slot_stride, const int32_t* positions, const int32_t* token_entry,
+                              const int32_t* entry_slot, const int32_t* entry_q_start, int num_tokens, int width,
+                              int taps, uintptr_t stream) {
+    if (num_tokens <= 0) return LLM_OK;
+    if (width <= 0 || taps < 1 || (taps > 1 && !kept)) return LLM_REFUSED_SIZE;
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    const bool four = width % 4 == 0;
+    const int per = four ? 4 : 1;
+    const dim3 grid(num_tokens, (width + CN_THREADS * per - 1) / (CN_THREADS * per));
+#define LAUNCH(TO, V)                                                                                           \
+    launch_pdl((short_conv_kernel<TO, V>), grid, dim3(CN_THREADS), 0, s, x, w, static_cast<TO*>(out), kept,      \
+               kept_slot_stride, positions, token_entry, entry_slot, entry_q_start, width, taps)
+    if (out_dtype == LLM_DT_F32) { if (four) LAUNCH(float, 4); else LAUNCH(float, 1); }
+    else if (out_dtype == LLM_DT_BF16) { if (four) LAUNCH(bf16, 4); else LAUNCH(bf16, 1); }
+    else return LLM_REFUSED_DTYPE;
+#undef LAUNCH
+    return launch_status();
+}
+
+// One block a token.  The row alpha * x + y is held in shared memory between the pass that sums its squares and the
+// pass that scales it.
+template <typename TY>
+__global__ void scaled_add_norm_kernel(
+    float* __restrict__ x, const TY* __restrict__ y, long long y_stride, int parts, long long part_stride,
+    const float* __restrict__ w, float alpha, float eps, float* __restrict__ kept, long long kept_slot_stride, int ring_rows,
+    const int32_t* __restrict__ positions, const int32_t* __restrict__ token_entry, const int32_t* __restrict__ entry_slot,
+    const int32_t* __restrict__ entry_q_start, const int32_t* __restrict__ entry_q_len, int width) {
+    pdl_begin();
+    extern __shared__ __align__(16) float row[];            // [width] + 33
+    float* scratch = row + width;
+    const int t = blockIdx.x;
+    float* xr = x + static_cast<size_t>(t) * width;
+    const TY* yr = y + static_cast<size_t>(t) * y_stride;
+    float* keep = nullptr;
+    if (kept && ring_rows > 0) {
+        const int e = token_entry[t];
+        if (t >= entry_q_start[e] + entry_q_len[e] - ring_rows)
+            keep = kept + static_cast<size_t>(entry_slot[e]) * kept_slot_stride +
+                   static_cast<size_t>(positions[t] % ring_rows) * width;
+    }
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float old = xr[i];
+        float add = 0.0f;
+        for (int z = 0; z < parts; ++z) add += to_f32(yr[z * part_stride + i]);
+        const float v = alpha * old + add;
+        if (keep) keep[i] = old;
+        row[i] = v;
+        ss += v * v;
+    }
+    const float total = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(total / static_cast<float>(width) + eps);
+    for (int i = threadIdx.x; i < width; i += blockDim.x) xr[i] = row[i] * inv * w[i];
+}
+
+extern "C" int llm_scaled_add_norm(float* x, const void* y, int y_dtype, long long y_stride, int parts,
+                                   long long part_stride, const float* w, float alpha, float eps, float* kept,
+                                   long long kept_slot_stride, int ring_rows, const int32_t* positions,
+                                   const int32_t* token_entry, const int32_t* entry_slot, const int32_t* entry_q_start,
+                                   const int32_t* entry_q_len, int num_tokens, int width, uintptr_t stream) {
+    if (num_tokens <= 0) return LLM_OK;
+    if (width <= 0 || parts < 1 || ring_rows < 0) return LLM_REFUSED_SIZE;
+    const size_t smem = (static_cast<size_t>(width) + 33) * sizeof(float);
+    if (smem > 200 * 1024) return LLM_REFUSED_SIZE;
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    const int threads = width >= 2048 ? 512 : CN_THREADS;
+#define LAUNCH(TY)                                                                                                 \
+    do {                                                                                                           \
+        auto kern = scaled_add_norm_kernel<TY>;                                                                    \
+        if (smem > 48 * 1024) {                                                                                    \
+            const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,          \
+                                                       static_cast<int>(smem));                                    \
+            if (e != cudaSuccess) return static_cast<int>(e);                                                      \
+        }                                                                                                          \
+        launch_pdl(kern, dim3(num_tokens), dim3(threads), smem, s, x, static_cast<const TY*>(y), y_stride, parts,  \
+                   part_stride, w, alpha, eps, kept, kept_slot_stride, ring_rows, positions, token_entry,          \
+                   entry_slot, entry_q_start, entry_q_len, width);                                                 \
+    } while (0)
+    if (y_dtype == LLM_DT_F32) LAUNCH(float);
+    else if (y_dtype == LLM_DT_BF16) LAUNCH(bf16);
+    else return LLM_REFUSED_DTYPE;
+#undef LAUNCH
+    return launch_status();
+}

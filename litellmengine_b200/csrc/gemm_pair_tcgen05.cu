@@ -135,6 +135,9 @@ __device__ __forceinline__ void gp_cluster_sync() {
     asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
 }
 __device__ __forceinline__ float gp_silu(float g) { return g / (1.0f + expf(-g)); }
+__device__ __forceinline__ float gp_gelu_tanh(float g) {
+    return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+}
 
 // The work of one cluster, in order: whole tiles c, c + C, ... below `whole` (a multiple of C), then the
 // remaining tiles cut `cut` ways along the features (units of 256 / cut accumulator columns), dealt
@@ -167,7 +170,9 @@ __device__ __forceinline__ bool gp_unit(const GpPlan& p, int i, int cluster, int
 
 // MODE 0: y[T, N] = x . w^T.  MODE 1: w is [gate; up] of 2 * inter rows, y[T, inter] = silu(gate) * up.
 // MODE 2: y[T, N] (float32) += x . w^T: the product joins the residual stream where it lies.
+// MODE 3: MODE 1 with the tanh form of gelu in place of silu (an instantiation of its own).
 // w_map, w_map2: the same weights read in boxes of 128 and 64 rows (for whole tiles and for halves).
+#define GP_GATED(MODE) ((MODE) == 1 || (MODE) == 3)
 template <int MODE, typename TO>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GP_THREADS, 1) linear_pair_tcgen05_kernel(
     const __grid_constant__ CUtensorMap x_map, const __grid_constant__ CUtensorMap w_map,
@@ -215,7 +220,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GP_THREADS, 1) linea
             for (int i = 0; ok && gp_unit(plan, i, cluster, clusters, &u); ++i) {
                 const int half = (GP_BN / 2) / u.cut;             // rows of w this CTA brings per stage
                 const int row_x = u.mt * (2 * GP_BM) + static_cast<int>(rank) * GP_BM;
-                const int row_w = MODE == 1 ? (rank == 0 ? 0 : inter) + u.nt * (GP_BN / 2) + u.part * half
+                const int row_w = GP_GATED(MODE) ? (rank == 0 ? 0 : inter) + u.nt * (GP_BN / 2) + u.part * half
                                             : u.nt * GP_BN + u.part * (2 * half) + static_cast<int>(rank) * half;
                 const CUtensorMap* wm = u.cut == 1 ? &w_map : &w_map2;
                 const unsigned bytes = 2u * (GP_BM + half) * GP_BK * sizeof(bf16);          // both CTAs' boxes
@@ -264,7 +269,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GP_THREADS, 1) linea
         const unsigned lane_addr = static_cast<unsigned>(quarter * 32) << 16;
         const unsigned acc_empty_first = gp_map_to(gp_smem(&acc_empty[0]), 0);
         float4* turn = reinterpret_cast<float4*>(b_s + GP_STAGES * TILE_ELEMS) + (warp - 2) * (32 * 8);    // [32 rows][8 chunks]
-        const int out_n = MODE == 1 ? inter : N;
+        const int out_n = GP_GATED(MODE) ? inter : N;
         GpUnit u;
         for (int i = 0; gp_unit(plan, i, cluster, clusters, &u); ++i) {
             const int buf = i & 1;
@@ -273,8 +278,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GP_THREADS, 1) linea
             const int tok0 = u.mt * (2 * GP_BM) + static_cast<int>(rank) * GP_BM + quarter * 32;       // the warp's first token
             const unsigned acc = tmem + lane_addr + buf * GP_BN;
             const int cols = GP_BN / u.cut;                       // accumulator columns of this unit
-            const int out_cols = MODE == 1 ? cols / 2 : cols;     // columns it writes
-            const int f0 = (MODE == 1 ? u.nt * (GP_BN / 2) : u.nt * GP_BN) + u.part * out_cols;
+            const int out_cols = GP_GATED(MODE) ? cols / 2 : cols;     // columns it writes
+            const int f0 = (GP_GATED(MODE) ? u.nt * (GP_BN / 2) : u.nt * GP_BN) + u.part * out_cols;
 #pragma unroll 1
             for (int c = 0; c < out_cols; c += 32) {
                 float v[32];
@@ -288,7 +293,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GP_THREADS, 1) linea
                                      : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
                     }
                 }
-                if (MODE == 1) {
+                if (GP_GATED(MODE)) {
                     unsigned g[32], up[32];
                     gp_ld32(acc + c, g);
                     gp_ld32(acc + out_cols + c, up);
@@ -297,7 +302,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GP_THREADS, 1) linea
                     for (int e = 0; e < 32; ++e) {
                         const float gate = __bfloat162float(__float2bfloat16_rn(__uint_as_float(g[e])));
                         const float upv = __bfloat162float(__float2bfloat16_rn(__uint_as_float(up[e])));
-                        v[e] = gp_silu(gate) * upv;
+                        v[e] = (MODE == 3 ? gp_gelu_tanh(gate) : gp_silu(gate)) * upv;
                     }
                 } else {
                     unsigned r[32];
@@ -428,7 +433,7 @@ static int gp_launch(const bf16* x, const bf16* w, void* y, int T, int N, int K,
         !gp_encode(&w_map2, w, w_rows, K, GP_BN / 4))
         return LLM_REFUSED_SIZE;
     const int tiles_m = (T + 2 * GP_BM - 1) / (2 * GP_BM);
-    const int tiles_n = MODE == 1 ? (inter + GP_BN / 2 - 1) / (GP_BN / 2) : (N + GP_BN - 1) / GP_BN;
+    const int tiles_n = GP_GATED(MODE) ? (inter + GP_BN / 2 - 1) / (GP_BN / 2) : (N + GP_BN - 1) / GP_BN;
     if (static_cast<long long>(tiles_m) * tiles_n > (1LL << 28)) return LLM_REFUSED_SIZE;
     GpPlan plan;
     int clusters;
@@ -463,11 +468,14 @@ extern "C" int llm_linear_pair(const void* x, const void* w, void* y, int out_dt
 
 // x: bfloat16 [T, K]; w: bfloat16 [2 * inter, K] = [gate; up]; y: bfloat16 [T, inter] = silu(gate) * up, gate and up
 // rounded to bfloat16 first.
-extern "C" int llm_linear_pair_silu_mul(const void* x, const void* w, void* y, int T, int inter, int K, int32_t* status,
-                                        uintptr_t stream) {
-    if (!llm_linear_pair_supported(T, inter, K)) return LLM_REFUSED_SIZE;
+extern "C" int llm_linear_pair_silu_mul(const void* x, const void* w, void* y, int T, int inter, int K, int act,
+                                        int32_t* status, uintptr_t stream) {
+    if (!llm_linear_pair_supported(T, inter, K) || act < 0 || act > 1) return LLM_REFUSED_SIZE;
     if (!aligned16(x) || !aligned16(w) || !aligned16(y) || status == nullptr) return LLM_REFUSED_ALIGN;
     if (!gp_ready()) return LLM_REFUSED_SIZE;
+    if (act == 1)               // the tanh form of gelu
+        return gp_launch<3, bf16>(static_cast<const bf16*>(x), static_cast<const bf16*>(w), y, T, inter, K, inter, 2LL * inter,
+                                  status, reinterpret_cast<cudaStream_t>(stream));
     return gp_launch<1, bf16>(static_cast<const bf16*>(x), static_cast<const bf16*>(w), y, T, inter, K, inter, 2LL * inter, status,
                               reinterpret_cast<cudaStream_t>(stream));
 }

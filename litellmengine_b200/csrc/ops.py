@@ -244,24 +244,29 @@ def rmsnorm_add(h: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: flo
     return copy
 
 
-def silu_and_mul(gate_up, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """[T, 2I] -> [T, I]: silu(first half) * second half.  A `PartialSum` is added up on the way."""
+ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+
+
+def silu_and_mul(gate_up, out: Optional[torch.Tensor] = None, activation: str = "silu") -> torch.Tensor:
+    """[T, 2I] -> [T, I]: act(first half) * second half, act = silu or the tanh form of gelu.  A `PartialSum` is
+    added up on the way."""
+    act = ACTIVATIONS[activation]
     if isinstance(gate_up, PartialSum):
         parts = gate_up.parts
         _dev(parts, out)
         S, T, two_i = parts.shape
         if out is None:
             out = torch.empty((T, two_i // 2), dtype=gate_up.rounds_to or torch.float32, device=parts.device)
-        f = _fn("activation", "llm_silu_and_mul_parts", [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p])
-        _check(f(_ptr(parts), S, _ptr(out), _dt(out), T, two_i // 2, _stream()), "silu_and_mul")
+        f = _fn("activation", "llm_silu_and_mul_parts", [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+        _check(f(_ptr(parts), S, _ptr(out), _dt(out), T, two_i // 2, act, _stream()), "silu_and_mul")
         return out
     _dev(gate_up, out)
     T, two_i = gate_up.shape
     inter = two_i // 2
     if out is None:
         out = torch.empty((T, inter), dtype=gate_up.dtype, device=gate_up.device)
-    f = _fn("activation", "llm_silu_and_mul", [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
-    _check(f(_ptr(gate_up), _ptr(out), _dt(gate_up), T, inter, _stream()), "silu_and_mul")
+    f = _fn("activation", "llm_silu_and_mul", [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(gate_up), _ptr(out), _dt(gate_up), T, inter, act, _stream()), "silu_and_mul")
     return out
 
 
@@ -493,19 +498,32 @@ def paged_attention_generic_kv(q: torch.Tensor, keys: torch.Tensor, values: torc
                                page_size: int, window: Optional[int], scale: float, status: torch.Tensor,
                                out: torch.Tensor, out_off: int = 0, gate: Optional[torch.Tensor] = None,
                                gate_off: int = 0, out_scale: float = 1.0, dist_bias: Optional[torch.Tensor] = None,
-                               gate_per_head: bool = False, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+                               gate_per_head: bool = False, rows: Optional[torch.Tensor] = None,
+                               head_scale: Optional[torch.Tensor] = None, log_bias=None,
+                               values_in_keys: bool = False) -> torch.Tensor:
     """Causal attention of every token in q [T, nq*dk] over its request's pages of `keys` [pages, nkv, page,
     dk] and `values` [pages, nkv, page, dv] (views with any page stride), written into columns out_off ..
     out_off + nq*dv of `out`, times sigmoid(gate[:, gate_off + ...]) (float32, optional; one value per output
     channel, or per head with `gate_per_head`) and `out_scale`.  `dist_bias` (float32 [len, nq]): row min(i - j,
     len - 1) is added to the scaled scores of query i and key j.  `rows` (int32): only these tokens are worked on
-    (-1 entries are padding)."""
-    _dev(q, positions, token_entry, entry_slot, block_table, status, dist_bias, rows)
+    (-1 entries are padding).  `head_scale` (float32 [nq]) multiplies each head's scaled scores; `log_bias` = (r1, r2),
+    float32 [nq] each, takes r1[h] * ln(1 + r2[h] * (i - j)) off them.  `values_in_keys`: `values` is None and the
+    values are the first dv entries of the key rows."""
+    r1, r2 = log_bias if log_bias is not None else (None, None)
+    _dev(q, positions, token_entry, entry_slot, block_table, status, dist_bias, rows, head_scale, r1, r2)
     _i32(rows, "rows")
+    for v in (head_scale, r1, r2):
+        if v is not None and (v.dtype != torch.float32 or v.numel() != nq):
+            raise KernelError("head_scale and the log bias's numbers must be float32 [heads]")
+    value_row = 0
+    if values_in_keys:
+        if values is not None or dv > dk:
+            raise KernelError("values_in_keys: no values tensor, and dv at most dk")
+        values, value_row = keys, dk
     if dist_bias is not None and (dist_bias.dtype != torch.float32 or dist_bias.dim() != 2 or dist_bias.shape[1] != nq):
         raise KernelError("dist_bias must be float32 [distances, heads]")
     T = q.shape[0]
-    for c, w in ((keys, dk), (values, dv)):
+    for c, w in ((keys, dk), (values, dk if values_in_keys else dv)):
         if (not c.is_cuda or c.dim() != 4 or tuple(c.shape[1:]) != (nkv, page_size, w)
                 or c[0].stride() != (page_size * w, w, 1)):
             raise KernelError("keys / values must be [pages, kv_heads, page_size, width] with dense pages")
@@ -516,15 +534,131 @@ def paged_attention_generic_kv(q: torch.Tensor, keys: torch.Tensor, values: torc
     f = _fn("attention_generic", "llm_paged_attention_generic_kv",
             [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_longlong, c_longlong, c_void_p, c_void_p, c_void_p,
              c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_longlong,
-             c_int, c_float, c_longlong, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p])
+             c_int, c_float, c_longlong, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+             c_longlong, c_void_p])
     _check(f(_ptr(q), _ptr(out), _dt(q), _ptr(keys), _ptr(values), _dt(keys), keys.stride(0), values.stride(0),
              _ptr(positions), _ptr(token_entry), _ptr(entry_slot), _ptr(block_table), block_table.shape[1],
              rows.numel() if rows is not None else T, nq, nkv,
              dk, dv, page_size, int(window) if window else 0, float(scale), keys.shape[0], _ptr(gate),
              gate.stride(0) if gate is not None else 0, gate_off, float(out_scale), out.stride(0), out_off,
              _ptr(status), _ptr(dist_bias), dist_bias.shape[0] if dist_bias is not None else 0,
-             1 if gate_per_head else 0, _ptr(rows), _stream()), "paged_attention_generic_kv")
+             1 if gate_per_head else 0, _ptr(rows), _ptr(head_scale), _ptr(r1), _ptr(r2), value_row, _stream()),
+           "paged_attention_generic_kv")
     return out
+
+
+# ---- a short convolution in front of a sublayer, the norm after the sum ------------------------------
+def short_conv(x: torch.Tensor, w: torch.Tensor, kept: Optional[torch.Tensor], batch, out_dtype: torch.dtype) -> torch.Tensor:
+    """u[t] = x[t] + sum_j w[:, j] * x_(t - taps + 1 + j) along each request's tokens, channel by channel, in 32-bit,
+    stored in `out_dtype`.  x: the float32 stream [T, W]; w: float32 [W, taps]; `kept`: float32 [slots, taps - 1, W]
+    (a view with any slot stride), the rows of the last taps - 1 positions of each request at ring row position mod
+    (taps - 1), read for tokens whose predecessors are not in this step; rows before a sequence's start are zero.
+    `batch` gives positions, token_entry, entry_slot, entry_q_start."""
+    _dev(x, w, batch.positions, batch.token_entry, batch.entry_slot, batch.entry_q_start)
+    T, W = x.shape
+    if x.dtype != torch.float32 or w.dtype != torch.float32 or w.dim() != 2 or w.shape[0] != W:
+        raise KernelError("short_conv wants a float32 stream [T, W] and float32 taps [W, taps]")
+    taps = w.shape[1]
+    if taps > 1 and (kept is None or kept.dtype != torch.float32 or tuple(kept.shape[1:]) != (taps - 1, W)
+                     or kept[0].stride() != (W, 1)):
+        raise KernelError("kept rows must be float32 [slots, taps - 1, W] with dense slots")
+    out = torch.empty((T, W), dtype=out_dtype, device=x.device)
+    f = _fn("conv_norm", "llm_short_conv",
+            [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+             c_int, c_void_p])
+    _check(f(_ptr(x), _ptr(w), _ptr(out), _dt(out), _ptr(kept) if taps > 1 else None, kept.stride(0) if taps > 1 else 0,
+             _ptr(batch.positions), _ptr(batch.token_entry), _ptr(batch.entry_slot), _ptr(batch.entry_q_start), T, W, taps,
+             _stream()), "short_conv")
+    return out
+
+
+def scaled_add_norm(x: torch.Tensor, y, weight: torch.Tensor, alpha: float, eps: float, kept: Optional[torch.Tensor],
+                    batch) -> torch.Tensor:
+    """x (float32 [T, W], in place) <- rmsnorm(alpha * x + y) * weight, row by row in 32-bit: the norm that follows
+    the sum.  y may be a `PartialSum`.  `kept` (float32 [slots, R, W], any slot stride): the OLD row of each token
+    among the last R of its portion is stored at ring row position mod R of its request (what the convolution in
+    front of the sublayer reads in the request's next step)."""
+    parts, part_stride = 1, 0
+    if isinstance(y, PartialSum):
+        if y.rounds_to is not None:
+            y = as_tensor(y)
+        else:
+            parts, part_stride = y.parts.shape[0], y.parts.stride(0)
+            y = y.parts[0]
+    _dev(x, weight)
+    T, W = x.shape
+    if not y.is_cuda or y.dim() != 2 or y.stride(1) != 1 or tuple(y.shape) != (T, W):
+        raise KernelError("y must be a CUDA matrix of x's shape with unit stride along its rows")
+    if x.dtype != torch.float32 or weight.dtype != torch.float32 or weight.numel() != W:
+        raise KernelError("scaled_add_norm wants a float32 stream and a float32 weight of the row length")
+    R = 0
+    if kept is not None:
+        R = kept.shape[1]
+        if kept.dtype != torch.float32 or kept.dim() != 3 or kept.shape[2] != W or (R and kept[0].stride() != (W, 1)):
+            raise KernelError("kept rows must be float32 [slots, R, W] with dense slots")
+    f = _fn("conv_norm", "llm_scaled_add_norm",
+            [c_void_p, c_void_p, c_int, c_longlong, c_int, c_longlong, c_void_p, c_float, c_float, c_void_p, c_longlong, c_int,
+             c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p])
+    _check(f(_ptr(x), _ptr(y), _dt(y), y.stride(0), parts, part_stride, _ptr(weight), float(alpha), float(eps),
+             _ptr(kept) if R else None, kept.stride(0) if R else 0, R, _ptr(batch.positions), _ptr(batch.token_entry),
+             _ptr(batch.entry_slot), _ptr(batch.entry_q_start), _ptr(batch.entry_q_len), T, W, _stream()), "scaled_add_norm")
+    return x
+
+
+# ---- latent attention ---------------------------------------------------------------------------
+def latent_prepare(proj: torch.Tensor, dq_off: int, dkv_off: int, Q: int, R: int, P: int, dims: int, wq: torch.Tensor,
+                   wkv: Optional[torch.Tensor], eps: float, inv_freq: Optional[torch.Tensor], keys: Optional[torch.Tensor],
+                   batch, block_table: Optional[torch.Tensor], page_size: int, status: torch.Tensor,
+                   q_dtype: torch.dtype) -> torch.Tensor:
+    """From the float32 projection [T, n] with the query latent in columns dq_off .. + Q and (if `keys`) the key/value
+    latent and the shared key part in columns dkv_off .. + R + P: returns rmsnorm(query latent) * wq as [T, Q] in
+    `q_dtype` and writes [rmsnorm(latent) * wkv | rotated key part] into the token's row of `keys` [pages, 1, page, R +
+    P].  The rotation turns the first `dims` entries of the key part (half-split pairs) by position * inv_freq."""
+    if proj.dtype != torch.float32 or proj.dim() != 2 or proj.stride(1) != 1 or not proj.is_cuda:
+        raise KernelError("proj must be a float32 CUDA matrix with unit stride along its rows")
+    _dev(wq, wkv, inv_freq, batch.positions, batch.token_entry, batch.entry_slot, block_table, status)
+    T, n = proj.shape
+    if dq_off + Q > n or (keys is not None and dkv_off + R + P > n):
+        raise KernelError("the projection is narrower than its pieces")
+    if wq.dtype != torch.float32 or wq.numel() != Q or (wkv is not None and (wkv.dtype != torch.float32 or wkv.numel() != R)):
+        raise KernelError("the latent norms' weights must be float32 of the latents' sizes")
+    if inv_freq is not None and (inv_freq.dtype != torch.float32 or inv_freq.numel() < dims // 2):
+        raise KernelError("inv_freq must be float32 [dims / 2]")
+    kps = pages = 0
+    if keys is not None:
+        if (not keys.is_cuda or keys.dim() != 4 or tuple(keys.shape[1:]) != (1, page_size, R + P)
+                or keys[0].stride() != (page_size * (R + P), R + P, 1) or block_table is None):
+            raise KernelError("keys must be [pages, 1, page_size, R + P] with dense pages, and come with a block table")
+        kps, pages = keys.stride(0), keys.shape[0]
+    cq = torch.empty((T, Q), dtype=q_dtype, device=proj.device)
+    f = _fn("latent_attention", "llm_latent_prepare",
+            [c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float, c_void_p, c_void_p,
+             c_int, c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p,
+             c_void_p])
+    _check(f(_ptr(proj), proj.stride(0), dq_off, dkv_off, Q, R, P, dims, _ptr(wq), _ptr(wkv), float(eps), _ptr(inv_freq),
+             _ptr(cq), _dt(cq), _ptr(keys), _dt(keys) if keys is not None else 0, kps, _ptr(batch.positions),
+             _ptr(batch.token_entry), _ptr(batch.entry_slot), _ptr(block_table),
+             block_table.shape[1] if block_table is not None else 0, T, page_size, pages, _ptr(status), _stream()),
+           "latent_prepare")
+    return cq
+
+
+def latent_q_split(q: torch.Tensor, positions: torch.Tensor, inv_freq: Optional[torch.Tensor], H: int, D: int, P: int,
+                   R: int, dims: int, dtype: torch.dtype):
+    """q: float32 [T, H * (D + P)], per head [D unrotated | P to rotate].  Returns (qn [H, T, D] in `dtype`, the
+    unrotated parts head-major; packed [T, H * (R + P)] in `dtype` whose columns R .. R + P of every head hold the
+    rotated parts and whose first R columns per head are left for the caller to fill)."""
+    _dev(q, positions, inv_freq)
+    T = q.shape[0]
+    if q.dtype != torch.float32 or q.shape[1] != H * (D + P):
+        raise KernelError("q must be float32 [T, heads * (D + P)]")
+    qn = torch.empty((H, T, D), dtype=dtype, device=q.device)
+    packed = torch.empty((T, H * (R + P)), dtype=dtype, device=q.device)
+    f = _fn("latent_attention", "llm_latent_q_split",
+            [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(q), _ptr(qn), _ptr(packed), _dt(qn), _ptr(positions), _ptr(inv_freq), T, H, D, P, R, dims, _stream()),
+           "latent_q_split")
+    return qn, packed
 
 
 # ---- gated linear attention ------------------------------------------------------------------
@@ -1231,8 +1365,9 @@ def linear_pair(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype,
     return out
 
 
-def linear_pair_silu_mul(x: torch.Tensor, w_gate_up: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """silu(x @ gate^T) * (x @ up^T) for w_gate_up = [gate; up] of 2 I rows, as bfloat16 [T, I]: the
+def linear_pair_silu_mul(x: torch.Tensor, w_gate_up: torch.Tensor, out: Optional[torch.Tensor] = None,
+                         activation: str = "silu") -> torch.Tensor:
+    """act(x @ gate^T) * (x @ up^T), act = silu or the tanh form of gelu, for w_gate_up = [gate; up] of 2 I rows, as bfloat16 [T, I]: the
     paired tcgen05 product with the activation in its epilogue (gate and up are rounded to bfloat16
     before the activation, as the separate kernel would read them)."""
     _dev(x, w_gate_up, out)
@@ -1244,8 +1379,10 @@ def linear_pair_silu_mul(x: torch.Tensor, w_gate_up: torch.Tensor, out: Optional
     inter = w_gate_up.shape[0] // 2
     if out is None:
         out = torch.empty((T, inter), dtype=torch.bfloat16, device=x.device)
-    f = _fn("gemm_pair_tcgen05", "llm_linear_pair_silu_mul", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p])
-    _check(f(_ptr(x), _ptr(w_gate_up), _ptr(out), T, inter, K, _ptr(stream_status(x.device)), _stream()), "linear_pair_silu_mul")
+    f = _fn("gemm_pair_tcgen05", "llm_linear_pair_silu_mul", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p,
+                                                              c_void_p])
+    _check(f(_ptr(x), _ptr(w_gate_up), _ptr(out), T, inter, K, ACTIVATIONS[activation], _ptr(stream_status(x.device)), _stream()),
+           "linear_pair_silu_mul")
     return out
 
 
@@ -1285,12 +1422,12 @@ def linear_into(x: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor) -
     return True
 
 
-def linear_silu_mul(x: torch.Tensor, w_gate_up: torch.Tensor, out_dtype: torch.dtype):
-    """silu(x @ gate^T) * (x @ up^T) for w_gate_up = [gate; up]: one kernel where the paired product
+def linear_silu_mul(x: torch.Tensor, w_gate_up: torch.Tensor, out_dtype: torch.dtype, activation: str = "silu"):
+    """act(x @ gate^T) * (x @ up^T) for w_gate_up = [gate; up]: one kernel where the paired product
     takes it, else the product (which may stay a sum of k-splits) followed by the activation kernel."""
     if out_dtype == torch.bfloat16 and _pair_takes(x, w_gate_up, w_gate_up.shape[0] // 2, "silu"):
-        return linear_pair_silu_mul(x, w_gate_up)
-    return silu_and_mul(linear(x, w_gate_up, out_dtype=out_dtype, partials_ok=True))
+        return linear_pair_silu_mul(x, w_gate_up, activation=activation)
+    return silu_and_mul(linear(x, w_gate_up, out_dtype=out_dtype, partials_ok=True), activation=activation)
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtype] = None,

@@ -237,7 +237,7 @@ class ModelRunner:
         # The warm-up below runs the step for real and the first replay runs it again.  Keys and values
         # land in the same places with the same values both times; a mixer's fixed-size state would be
         # advanced twice, so it is put back in between.
-        states = {k: t.clone() for k, t in self.cache.state.items() if isinstance(k, int)}
+        states = {k: t.clone() for k, t in self.cache.state.items() if not isinstance(k, str)}      # the stages' own
         with torch.cuda.stream(side):           # warm every kernel and library handle outside capture
             self.model.forward(batch, self.cache)
             for k, t in states.items():

@@ -1,5 +1,5 @@
 """Parts a model is assembled from, and the model that runs them."""
-from . import norms, position, attention, linear_attention, parallel, feed_forward, block     # registers the built-in kinds
+from . import norms, position, attention, linear_attention, latent_attention, parallel, feed_forward, block     # registers the built-in kinds
 from .registry import (lookup, register_arrangement, register_feed_forward, register_mixer,
                        register_norm, register_position, unregister)
 from .context import StageContext, StepFacts, StepPrelude

@@ -226,14 +226,17 @@ class GatedAttentionMixer(BranchMixer):
     to their pages; the attention kernel applies the gate as it stores.  The gate may be one value per head
     (`output_gate_scope` 'head').  `distance_bias` = (rows, far) adds a learned bias table[bucket(i - j), head]
     to the scaled score of query i and key j (see `distance_bucket`); the mixer expands the stored table
-    [rows, heads] into one row per distance once, when it is loaded."""
+    [rows, heads] into one row per distance once, when it is loaded.  `head_temperature`: a learned number per query
+    head multiplies the scaled score; `log_distance_bias`: r1[h] * ln(1 + r2[h] * (i - j)) is taken off it (two learned
+    numbers per query head, evaluated inside the attention kernel: no table, no farthest distance)."""
 
     graph_safe = True
     any_division_safe = True
 
     _DEFAULT_NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "g": "g_proj.weight",
                       "o": "o_proj.weight", "q_bias": "q_proj.bias", "k_bias": "k_proj.bias", "v_bias": "v_proj.bias",
-                      "q_norm": "q_norm.weight", "k_norm": "k_norm.weight", "rel": "distance_bias"}
+                      "q_norm": "q_norm.weight", "k_norm": "k_norm.weight", "rel": "distance_bias",
+                      "temp": "head_temperature", "r1": "log_bias.r1", "r2": "log_bias.r2"}
 
     def __init__(self, spec: MixerSpec, hidden_size: int, compute_dtype: torch.dtype, device):
         if spec.num_heads <= 0 or spec.num_kv_heads <= 0 or spec.num_heads % spec.num_kv_heads:
@@ -273,12 +276,14 @@ class GatedAttentionMixer(BranchMixer):
                 raise ValueError("distance_bias: the farthest distance must exceed half the number of rows")
         # the tuned bfloat16 kernels read keys and values of one width from one tensor, add no bias to the
         # scores and leave the gate to a kernel that takes one value per channel
+        self.head_temp = self.log_r1 = self.log_r2 = None     # float32 [heads] each, when the spec asks for them
+        scored = spec.head_temperature or spec.log_distance_bias      # the scores carry more than the tuned kernels know
         self._tuned = (compute_dtype == torch.bfloat16 and self.dv == self.d and self.device.type == "cuda"
-                       and spec.distance_bias is None and not self.gate_per_head
+                       and spec.distance_bias is None and not self.gate_per_head and not scored
                        and ops.fast_attention_supported(self.d, self.nq // self.nkv))
         # with a bias by distance or a gate per head: prompt portions still take a tensor-core kernel (the
         # mma.sync one, which adds the bias to its scores and gates as it stores), single tokens the general one
-        self._tuned_prompt = (not self._tuned and compute_dtype == torch.bfloat16 and self.dv == self.d
+        self._tuned_prompt = (not self._tuned and not scored and compute_dtype == torch.bfloat16 and self.dv == self.d
                               and self.device.type == "cuda" and (self.gate_per_head or not spec.output_gate)
                               and ops.prefill_attention_supported(self.d))
         self._tuned_decode = self._tuned_prompt and ops.fast_attention_supported(self.d, self.nq // self.nkv)
@@ -292,6 +297,11 @@ class GatedAttentionMixer(BranchMixer):
             p[n["g"]] = ParamSpec((self.gate_width, self.hidden))
         if s.distance_bias is not None:
             p[n["rel"]] = ParamSpec((s.distance_bias[0], self.nq), role="scale", init=("normal", 0.5))
+        if s.head_temperature:
+            p[n["temp"]] = ParamSpec((self.nq,), role="scale", init=("one_plus_normal", 0.2))
+        if s.log_distance_bias:
+            p[n["r1"]] = ParamSpec((self.nq,), role="scale", init=("one_plus_normal", 0.15))
+            p[n["r2"]] = ParamSpec((self.nq,), role="scale", init=("one_plus_normal", 0.15))     # stays positive
         if s.bias:
             for key, size in (("q_bias", self.nq * self.d), ("k_bias", self.nkv * self.d), ("v_bias", self.nkv * self.dv)):
                 p[n[key]] = ParamSpec((size,), role="scale", init=("normal", 0.02))
@@ -311,6 +321,10 @@ class GatedAttentionMixer(BranchMixer):
             self.biases = tuple(t[n[k]].contiguous() for k in ("q_bias", "k_bias", "v_bias"))
         if s.qk_norm is not None:
             self.q_norm_w, self.k_norm_w = t[n["q_norm"]].contiguous(), t[n["k_norm"]].contiguous()
+        if s.head_temperature:
+            self.head_temp = t[n["temp"]].float().contiguous()
+        if s.log_distance_bias:
+            self.log_r1, self.log_r2 = t[n["r1"]].float().contiguous(), t[n["r2"]].float().contiguous()
         if s.distance_bias is not None:
             rel = t[n["rel"]].float()
             rows, far = rel.shape[0], float(s.distance_bias[1])
@@ -397,7 +411,8 @@ class GatedAttentionMixer(BranchMixer):
             q, ctx.cache_keys, ctx.cache_values, b.positions, b.token_entry, b.entry_slot, ctx.block_table, self.nq,
             self.nkv, self.d, self.dv, ctx.page_size, s.window, self.scale, ctx.status, out, out_col0,
             gate=proj if s.output_gate else None, gate_off=col0 + self.g_off, out_scale=out_scale,
-            dist_bias=self.dist_table, gate_per_head=self.gate_per_head, rows=rows)
+            dist_bias=self.dist_table, gate_per_head=self.gate_per_head, rows=rows, head_scale=self.head_temp,
+            log_bias=(self.log_r1, self.log_r2) if self.log_r1 is not None else None)
 
 
 def distance_bucket(n: int, rows: int, far: float) -> int:

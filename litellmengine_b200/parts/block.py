@@ -57,8 +57,32 @@ def streams_norm(streams: torch.Tensor, pending: Optional[PendingUpdate], inp: O
                            norm.eps, getattr(norm, "center", False), out_dtype, rows=rows, fan=fan)
 
 
+class InputConvolution:
+    """What a sublayer reads instead of the stream x itself: u_t = x_t + sum_j w[:, j] * x_(t - taps + 1 + j), a causal
+    convolution over time on each channel (`w` [hidden, taps], the last tap on the token itself, zeros before the
+    sequence's start), in 32-bit, stored in the compute dtype.  The last taps - 1 rows of x are kept per request."""
+
+    def __init__(self, hidden_size: int, taps: int):
+        if taps < 1:
+            raise ValueError("an input convolution needs at least one tap")
+        self.hidden, self.taps = hidden_size, taps
+        self.weight: Optional[torch.Tensor] = None
+
+    def parameters(self) -> Dict[str, ParamSpec]:
+        return {"": ParamSpec((self.hidden, self.taps), role="scale", init=("normal", 0.2))}
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        self.weight = tensors[""].contiguous()
+
+    def forward(self, x: torch.Tensor, kept: Optional[torch.Tensor], batch, out_dtype: torch.dtype) -> torch.Tensor:
+        from ..csrc import ops
+        return ops.short_conv(x, self.weight, kept, batch, out_dtype)
+
+
 class Block:
     """Holds one layer's mixer, feed-forward and norms, each chosen by the layer's spec."""
+
+    STATE_NAME = "block"          # the name of the state a layer's arrangement keeps per request, beside its mixer's
 
     def __init__(self, spec: BlockSpec, hidden_size: int, compute_dtype: torch.dtype, device):
         self.spec = spec
@@ -79,6 +103,24 @@ class Block:
         if spec.connections is not None:
             n = spec.connections[0]
             self.connections = (StreamConnection(n), StreamConnection(n) if self.feed_forward is not None else None)
+        # a causal convolution over time in front of each sublayer
+        self.input_convs = None
+        taps = getattr(spec, "input_conv", None)
+        if taps is not None:
+            self.input_convs = (InputConvolution(hidden_size, taps),
+                                InputConvolution(hidden_size, taps) if self.feed_forward is not None else None)
+        self.residual_scale = float(getattr(spec, "residual_scale", 1.0))
+        self.hidden = hidden_size
+
+    def state_need(self):
+        """What the layer keeps per request beside its mixer's cache: the last taps - 1 rows of the stream in front of
+        each sublayer that reads it through a convolution, [sublayers, taps - 1, hidden] float32 (ring rows by
+        position); None without a convolution or with a single tap."""
+        from ..cache import StateNeed
+        if self.input_convs is None or self.input_convs[0].taps < 2:
+            return None
+        subs = 2 if self.feed_forward is not None else 1
+        return StateNeed((subs, self.input_convs[0].taps - 1, self.hidden), "float32", name=self.STATE_NAME)
 
     def _children(self):
         s = self.spec
@@ -87,6 +129,8 @@ class Block:
             out += [(s.feed_forward_norm_name, self.feed_forward_norm), (s.feed_forward.weight_prefix, self.feed_forward)]
         if self.connections is not None:
             out += [(name, c) for name, c in zip(s.connections[1:], self.connections) if c is not None]
+        if self.input_convs is not None:
+            out += [(name, c) for name, c in zip(s.input_conv_names, self.input_convs) if c is not None]
         return out
 
     def parts(self):
@@ -174,6 +218,35 @@ def branch_norm(block: Block, h: torch.Tensor, delta: Optional[torch.Tensor], ct
         x = block.feed_forward_norm.add_normed(h, f, narrow)
     if narrow is not None:
         tables["stream_copy"] = (h, x)
+    return h, None
+
+
+@register_arrangement("post_norm")
+def post_norm(block: Block, h: torch.Tensor, delta: Optional[torch.Tensor], ctx: StageContext):
+    """h <- norm1(a * h + mixer(u(h))); h <- norm2(a * h + ffn(u(h))) with a = the layer's `residual_scale`: the norm
+    follows the sum and the sublayers read the stream itself, through the layer's input convolution if it has one
+    (u = h + conv(h), else u = h).  `h` is the float32 residual stream, complete on entry and on return.  The kernel
+    of the norm also keeps the rows the convolution will want in the request's next step."""
+    from ..csrc import ops
+    if delta is not None:
+        ops.residual_add(h, ops.as_tensor(delta))
+    b, kept = ctx.batch, ctx.block_state
+
+    def read(sub: int):
+        if block.input_convs is not None:
+            return block.input_convs[sub].forward(h, kept[:, sub] if kept is not None else None, b, block.dtype)
+        return h if block.dtype == torch.float32 else h.to(block.dtype)
+
+    ctx.partials_ok = True                                      # the norm kernel adds a product's k-splits as it reads
+    ctx.residual = None                                         # the norm stands between the product and the stream
+    a = block.mixer.forward(read(0), ctx)
+    ops.scaled_add_norm(h, a, block.mixer_norm.weight, block.residual_scale, block.mixer_norm.eps,
+                        kept[:, 0] if kept is not None else None, b)
+    if block.feed_forward is not None:
+        extra = {"partials_ok": True} if getattr(block.feed_forward, "supports_partials", False) else {}
+        f = block.feed_forward.forward(read(1), **extra)
+        ops.scaled_add_norm(h, f, block.feed_forward_norm.weight, block.residual_scale, block.feed_forward_norm.eps,
+                            kept[:, 1] if kept is not None else None, b)
     return h, None
 
 

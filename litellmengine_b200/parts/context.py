@@ -62,6 +62,7 @@ class StageContext:
     block_table  device int32 [slots, pages per request] of the cache's group.
     writes_cache False when the cache belongs to another stage.
     state        [slots, *shape] tensor if the mixer asked for fixed-size state, else None.
+    block_state  [slots, *shape] tensor if the layer itself (its arrangement, not its mixer) asked for state.
     status       device int32 [2] where kernels record a refused index instead of trapping.
     partials_ok  True when whoever consumes the mixer's output adds up an `ops.PartialSum`
                  itself, so the mixer may return one instead of a tensor.
@@ -81,3 +82,4 @@ class StageContext:
     residual: Optional[torch.Tensor] = None
     cache_keys: Optional[torch.Tensor] = None
     cache_values: Optional[torch.Tensor] = None
+    block_state: Optional[torch.Tensor] = None

@@ -13,8 +13,9 @@ from .registry import register_feed_forward
 
 @register_feed_forward("swiglu")
 class SwiGLU:
-    """down(silu(gate(x)) * up(x)), no biases (src/model/qwen3.cpp:143-152,
-    src/ops/silu_and_mul.cu:44-46).  Gate and up are one fused product [g | u]."""
+    """down(act(gate(x)) * up(x)), no biases, act = silu (src/model/qwen3.cpp:143-152,
+    src/ops/silu_and_mul.cu:44-46) or what the spec's `params` name as `activation` ('gelu_tanh').  Gate and up are
+    one fused product [g | u]."""
 
     graph_safe = True          # forward only launches kernels on the current stream
     any_division_safe = True   # and nothing in it is shaped by the number of entries of the step
@@ -26,6 +27,9 @@ class SwiGLU:
         names = dict(getattr(spec, "tensor_names", ()))
         self._gate, self._up, self._down = (names.get("gate", "gate_proj.weight"), names.get("up", "up_proj.weight"),
                                             names.get("down", "down_proj.weight"))
+        self.activation = dict(getattr(spec, "params", ())).get("activation", "silu")
+        if self.activation not in ops.ACTIVATIONS:
+            raise ValueError(f"activation {self.activation!r}: one of {sorted(ops.ACTIVATIONS)}")
         self.w_gate_up: Optional[torch.Tensor] = None
         self.w_down: Optional[torch.Tensor] = None
 
@@ -46,7 +50,7 @@ class SwiGLU:
     supports_residual = True   # forward(x, residual=h) may add its result to h itself and return None
 
     def forward(self, x: torch.Tensor, partials_ok: bool = False, residual: Optional[torch.Tensor] = None):
-        act = ops.linear_silu_mul(x, self.w_gate_up, self.dtype)
+        act = ops.linear_silu_mul(x, self.w_gate_up, self.dtype, self.activation)
         if residual is not None and ops.linear_into(act, self.w_down, residual):
             return None                                                               # joined the residual in the product
         return ops.linear(act, self.w_down, out_dtype=torch.float32, partials_ok=partials_ok)

@@ -81,10 +81,12 @@ class Model:
     def stage_needs(self) -> list:
         needs = []
         for st in self.plan.order:
-            if st.cache_from is not None:
-                needs.append(("borrow", st.cache_from))
-            else:
-                needs.append(self.blocks[st.block].mixer.cache_need())
+            block = self.blocks[st.block]
+            need = ("borrow", st.cache_from) if st.cache_from is not None else block.mixer.cache_need()
+            own = block.state_need()                  # what the layer's arrangement keeps per request, beside its mixer
+            if own is not None:
+                need = [n for n in (need if isinstance(need, list) else [need]) if n is not None] + [own]
+            needs.append(need)
         return needs
 
     def step_preludes(self) -> list:
@@ -129,7 +131,7 @@ class Model:
         for b in self.blocks:
             for part in b.parts():
                 for v in vars(part).values():
-                    if isinstance(v, torch.Tensor) and v.dim() == 2:
+                    if isinstance(v, torch.Tensor) and v.dim() in (2, 3):
                         add(v)
         add(self.output)
         return total
@@ -172,7 +174,7 @@ class Model:
             keys, values = cache.stage_pages(s)
         return StageContext(batch=batch, stage=s, cache=kv, block_table=table, page_size=cache.page_size,
                             writes_cache=st.cache_from is None, state=cache.state.get(s), status=batch.status,
-                            cache_keys=keys, cache_values=values)
+                            cache_keys=keys, cache_values=values, block_state=cache.state.get((s, Block.STATE_NAME)))
 
 
 def model_parameters(plan: ModelPlan) -> Dict[str, ParamSpec]:
