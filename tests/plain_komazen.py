@@ -135,7 +135,9 @@ def latent_attention(u, w, pre, m, eps, act=identity, shared=None):
     s = (torch.einsum("thd,shd->hts", act(qn), act(kn)) + torch.einsum("thd,sd->hts", act(qr), kr)) * m["scale"]
     i = torch.arange(T)[:, None]
     j = torch.arange(T)[None, :]
-    visible = (j <= i) & (i - j < m["mask"]["size"])
+    visible = j <= i
+    if m.get("mask") is not None:
+        visible = visible & (i - j < m["mask"]["size"])
     o = softmax_core(s, act(v).permute(1, 0, 2), visible).permute(1, 0, 2).reshape(T, H * V)
     gate = torch.sigmoid(x @ w[pre + "g"].T)
     return act(o * gate) @ w[pre + "o"].T
