@@ -77,6 +77,14 @@ __global__ void __launch_bounds__(AD_THREADS) paged_decode_attention_kernel(
     const int split = blockIdx.x, kvh = blockIdx.y, r = blockIdx.z;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int G = nq / nkv, h0 = kvh * G;
+    float an0[3] = {1.0f, 0.0f, 0.0f}, an1[3] = {1.0f, 0.0f, 0.0f};      // this lane's two heads: temperature, r1, r2
+    if (BIAS && dist_len < 0) {
+#pragma unroll
+        for (int u = 0; u < 3; ++u) {
+            an0[u] = dist_bias[(h0 + min(threadIdx.x % 32 >> 2, G - 1)) * 3 + u];
+            an1[u] = dist_bias[(h0 + min((threadIdx.x % 32 >> 2) + 8, G - 1)) * 3 + u];
+        }
+    }
     const int t = rows ? rows[r] : r;
     if (t < 0) return;                                              // a padding entry of the row list: no work
     const int pos = positions[t];
@@ -182,10 +190,15 @@ __global__ void __launch_bounds__(AD_THREADS) paged_decode_attention_kernel(
                 const int key = key0 + nb * 8 + (lane & 3) * 2 + c;
                 const bool vis = key < k_end;
                 float a0 = s[nb][c] * scale_log2e, a1 = s[nb][2 + c] * scale_log2e;
-                if (BIAS && vis) {               // a learned bias by distance: a row of [heads, distances] per head, exp2 domain
+                if (BIAS && vis && dist_len > 0) {     // a learned bias by distance: a row of [heads, distances] per head, exp2 domain
                     const int dist = min(max(pos - key, 0), dist_len - 1);
                     a0 += __ldg(dist_bias + static_cast<size_t>(h0 + min(lane >> 2, G - 1)) * dist_len + dist);
                     a1 += __ldg(dist_bias + static_cast<size_t>(h0 + min((lane >> 2) + 8, G - 1)) * dist_len + dist);
+                }
+                if (BIAS && vis && dist_len < 0) {     // (temperature, r1, r2) per head: a0 * temperature - r1 * log2(1 + r2 * distance)
+                    const float far = static_cast<float>(max(pos - key, 0));
+                    a0 = a0 * an0[0] - an0[1] * __log2f(1.0f + an0[2] * far);
+                    a1 = a1 * an1[0] - an1[1] * __log2f(1.0f + an1[2] * far);
                 }
                 s[nb][c] = vis ? a0 : -CUDART_INF_F;
                 s[nb][2 + c] = vis ? a1 : -CUDART_INF_F;
@@ -359,14 +372,16 @@ extern "C" long long llm_paged_decode_scratch_floats(int n_rows, int nq, int d, 
 // q, out: bfloat16 [T, nq*d]; cache: bfloat16 [pages, 2, nkv, page_size, d]; rows: int32 [n_rows] token
 // rows to attend for (null: rows 0..n_rows-1); scratch: float32, llm_paged_decode_scratch_floats long.
 // `dist_bias` float32 [nq, dist_len] (optional): a learned bias by distance in the exp2 domain (the table times
-// log2 e); row min(p - j, dist_len - 1) of a head joins the scaled score of the query at p and key j.
+// log2 e); row min(p - j, dist_len - 1) of a head joins the scaled score of the query at p and key j.  dist_len == -1:
+// `dist_bias` is float32 [nq, 3], per head a temperature on the scaled score and the two numbers of the bias
+// r1 * ln(1 + r2 * (p - j)) that is taken off it.
 extern "C" int llm_paged_attention_decode_biased(
     const void* q, void* out, const void* cache, const int32_t* rows, int n_rows, const int32_t* positions,
     const int32_t* token_entry, const int32_t* entry_slot, const int32_t* block_table, int table_stride, int nq,
     int nkv, int d, int page_size, int window, float scale, int num_pages, int num_splits, float* scratch,
     int32_t* status, const float* dist_bias, int dist_len, uintptr_t stream) {
     if (n_rows <= 0) return LLM_OK;
-    if (dist_bias && dist_len <= 0) return LLM_REFUSED_SIZE;
+    if (dist_bias && dist_len <= 0 && dist_len != -1) return LLM_REFUSED_SIZE;
     if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || page_size <= 0 || num_splits < 1 || num_splits > 65535 ||
         nkv > 65535 || n_rows > 65535)
         return LLM_REFUSED_SIZE;

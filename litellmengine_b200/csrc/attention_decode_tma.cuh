@@ -91,6 +91,14 @@ __global__ void __launch_bounds__(AD_THREADS + 32) paged_decode_attention_tma_ke
     const int split = blockIdx.x, kvh = blockIdx.y, r = blockIdx.z;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int G = nq / nkv, h0 = kvh * G;
+    float an0[3] = {1.0f, 0.0f, 0.0f}, an1[3] = {1.0f, 0.0f, 0.0f};      // this lane's two heads: temperature, r1, r2
+    if (BIAS && dist_len < 0) {
+#pragma unroll
+        for (int u = 0; u < 3; ++u) {
+            an0[u] = dist_bias[(h0 + min(threadIdx.x % 32 >> 2, G - 1)) * 3 + u];
+            an1[u] = dist_bias[(h0 + min((threadIdx.x % 32 >> 2) + 8, G - 1)) * 3 + u];
+        }
+    }
     const int t = rows ? rows[r] : r;
     if (t < 0) return;                                              // a padding entry of the row list: no work
     const int pos = positions[t];
@@ -217,10 +225,15 @@ __global__ void __launch_bounds__(AD_THREADS + 32) paged_decode_attention_tma_ke
                     const int key = key0 + nb * 8 + (lane & 3) * 2 + c;
                     const bool vis = key < k_end && key >= k_begin;
                     float a0 = s[nb][c] * scale_log2e, a1 = s[nb][2 + c] * scale_log2e;
-                    if (BIAS && vis) {           // a learned bias by distance: a row of [heads, distances] per head, exp2 domain
+                    if (BIAS && vis && dist_len > 0) {     // a learned bias by distance: a row of [heads, distances] per head, exp2 domain
                         const int dist = min(max(pos - key, 0), dist_len - 1);
                         a0 += __ldg(dist_bias + static_cast<size_t>(h0 + min(lane >> 2, G - 1)) * dist_len + dist);
                         a1 += __ldg(dist_bias + static_cast<size_t>(h0 + min((lane >> 2) + 8, G - 1)) * dist_len + dist);
+                    }
+                    if (BIAS && vis && dist_len < 0) {     // (temperature, r1, r2) per head: a0 * temperature - r1 * log2(1 + r2 * distance)
+                        const float far = static_cast<float>(max(pos - key, 0));
+                        a0 = a0 * an0[0] - an0[1] * __log2f(1.0f + an0[2] * far);
+                        a1 = a1 * an1[0] - an1[1] * __log2f(1.0f + an1[2] * far);
                     }
                     s[nb][c] = vis ? a0 : -CUDART_INF_F;
                     s[nb][2 + c] = vis ? a1 : -CUDART_INF_F;

@@ -148,7 +148,12 @@ __global__ void __launch_bounds__(AP_THREADS) paged_prefill_attention_kernel(
     const int lo1 = (window > 0 && pos1 - window + 1 > 0) ? pos1 - window + 1 : 0;
     const bool live0 = r0 < rows_here, live1 = r0 + 8 < rows_here;
     // a learned bias by distance, one row of [heads, distances] per head, already in the exp2 domain
-    const float* bias_h = (EXT && dist_bias) ? dist_bias + static_cast<size_t>(h) * dist_len : nullptr;
+    const float* bias_h = (EXT && dist_bias && dist_len > 0) ? dist_bias + static_cast<size_t>(h) * dist_len : nullptr;
+    // dist_len == -1: no table but three numbers per head, (temperature, r1, r2): the scaled score is multiplied by the
+    // temperature and r1 * log2(1 + r2 * distance) is taken off it (the exp2 domain's r1 * ln(1 + r2 * distance))
+    const bool analytic = EXT && dist_bias && dist_len < 0;
+    const float br1 = analytic ? dist_bias[h * 3 + 1] : 0.0f, br2 = analytic ? dist_bias[h * 3 + 2] : 0.0f;
+    if (analytic) scale_log2e *= dist_bias[h * 3];
     if (!EXT) {
         out_scale = 1.0f;
         out_stride = static_cast<long long>(nq) * D;
@@ -213,6 +218,10 @@ __global__ void __launch_bounds__(AP_THREADS) paged_prefill_attention_kernel(
                 if (EXT && bias_h) {
                     a += __ldg(bias_h + min(max(pos0 - key, 0), dist_len - 1));
                     b2 += __ldg(bias_h + min(max(pos1 - key, 0), dist_len - 1));
+                }
+                if (EXT && analytic) {
+                    a -= br1 * __log2f(1.0f + br2 * static_cast<float>(max(pos0 - key, 0)));
+                    b2 -= br1 * __log2f(1.0f + br2 * static_cast<float>(max(pos1 - key, 0)));
                 }
                 if (need_mask) {
                     if (key > pos0 || key < lo0) a = -CUDART_INF_F;
@@ -307,7 +316,8 @@ extern "C" int llm_paged_attention_prefill(
 
 // The same with what other attention layers add: `dist_bias` float32 [nq, dist_len], a learned bias by distance in
 // the exp2 domain (the table times log2 e), row min(i - j, dist_len - 1) of a head added to the scaled score of
-// query i and key j; `head_gate` float32, one value per (token, head) at [token * gate_stride + gate_off + head],
+// query i and key j (dist_len == -1: `dist_bias` is float32 [nq, 3] = a temperature on the scaled score and the two
+// numbers of the bias r1 * ln(1 + r2 * (i - j)) that is taken off it, per head); `head_gate` float32, one value per (token, head) at [token * gate_stride + gate_off + head],
 // whose sigmoid multiplies the head's output; `out_scale`; the output row as a column range of a wider buffer.
 extern "C" int llm_paged_attention_prefill_ex(
     const void* q, void* out, const void* cache, const int32_t* tiles, int n_tiles, const int32_t* entry_slot,
@@ -317,7 +327,7 @@ extern "C" int llm_paged_attention_prefill_ex(
     int gate_off, float out_scale, long long out_stride, int out_off, uintptr_t stream) {
     if (n_tiles <= 0) return LLM_OK;
     if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || page_size <= 0 || !llm_paged_prefill_supported(d)) return LLM_REFUSED_SIZE;
-    if (dist_bias && dist_len <= 0) return LLM_REFUSED_SIZE;
+    if (dist_bias && dist_len <= 0 && dist_len != -1) return LLM_REFUSED_SIZE;
     if (!aligned16(q) || !aligned16(out) || !aligned16(cache) || out_stride % 2 || out_off % 2) return LLM_REFUSED_ALIGN;
     const size_t smem = static_cast<size_t>(AP_BM + 4 * AP_BN) * d * sizeof(bf16);
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);

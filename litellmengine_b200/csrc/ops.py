@@ -1030,13 +1030,17 @@ def decode_scratch(device, floats: int) -> Optional[torch.Tensor]:
 def paged_attention_decode(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, rows: Optional[torch.Tensor],
                            n_rows: int, positions, token_entry, entry_slot, block_table: torch.Tensor, nq: int,
                            nkv: int, d: int, page_size: int, window: Optional[int], scale: float, num_splits: int,
-                           status: torch.Tensor, dist_bias_t: Optional[torch.Tensor] = None) -> torch.Tensor:
+                           status: torch.Tensor, dist_bias_t: Optional[torch.Tensor] = None,
+                           analytic_bias: bool = False) -> torch.Tensor:
     """Attention for single decoded tokens (rows of q named by `rows`, or rows 0..n_rows-1), written
     into the same rows of `out`.  bfloat16 only.  `dist_bias_t` float32 [nq, distances]: a bias by distance TIMES
     log2(e); row min(p - j, distances - 1) of a head joins the scaled score of the query at p and key j."""
     _dev(q, out, cache, rows, positions, token_entry, entry_slot, block_table, status, dist_bias_t)
     if dist_bias_t is not None and (dist_bias_t.dtype != torch.float32 or dist_bias_t.dim() != 2 or dist_bias_t.shape[0] != nq):
         raise KernelError("dist_bias_t must be float32 [heads, distances]")
+    dist_len = 0 if dist_bias_t is None else (-1 if analytic_bias else dist_bias_t.shape[1])
+    if analytic_bias and (dist_bias_t is None or dist_bias_t.shape[1] != 3):
+        raise KernelError("an analytic bias comes as float32 [heads, 3]: temperature, r1, r2")
     if q.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
         raise KernelError("the decode attention kernel is bfloat16 only")
     if q.shape[1] != nq * d or tuple(cache.shape[1:]) != (2, nkv, page_size, d):
@@ -1050,7 +1054,7 @@ def paged_attention_decode(q: torch.Tensor, out: torch.Tensor, cache: torch.Tens
     _check(f(_ptr(q), _ptr(out), _ptr(cache), _ptr(rows), n_rows, _ptr(positions), _ptr(token_entry),
              _ptr(entry_slot), _ptr(block_table), block_table.shape[1], nq, nkv, d, page_size,
              int(window) if window else 0, float(scale), cache.shape[0], num_splits, _ptr(scratch), _ptr(status),
-             _ptr(dist_bias_t), dist_bias_t.shape[1] if dist_bias_t is not None else 0, _stream()), "paged_attention_decode")
+             _ptr(dist_bias_t), dist_len, _stream()), "paged_attention_decode")
     if num_splits > 1:
         global launch_count
         launch_count += 1                         # the merge kernel
@@ -1090,8 +1094,10 @@ def paged_attention_prefill_biased(q: torch.Tensor, out: torch.Tensor, out_off: 
                                    block_table: torch.Tensor, nq: int, nkv: int, d: int, page_size: int,
                                    window: Optional[int], scale: float, status: torch.Tensor,
                                    dist_bias_t: Optional[torch.Tensor] = None, head_gate: Optional[torch.Tensor] = None,
-                                   gate_off: int = 0, out_scale: float = 1.0) -> torch.Tensor:
-    """`paged_attention_prefill` with what other attention layers add: `dist_bias_t` float32 [nq, distances], a bias by
+                                   gate_off: int = 0, out_scale: float = 1.0, analytic_bias: bool = False) -> torch.Tensor:
+    """`analytic_bias`: `dist_bias_t` is float32 [nq, 3], per head a temperature on the scaled score and the numbers
+    r1, r2 of the bias r1 * ln(1 + r2 * (i - j)) that is taken off it (evaluated in the kernel; no table).
+    `paged_attention_prefill` with what other attention layers add: `dist_bias_t` float32 [nq, distances], a bias by
     distance TIMES log2(e) (row min(i - j, distances - 1) of the head joins the scaled score); `head_gate` float32
     [T, ...] with one value per (token, head) from column gate_off, whose sigmoid multiplies the head's output;
     `out_scale`; the result goes to columns out_off .. out_off + nq*d of `out` (bfloat16, any row stride)."""
@@ -1102,6 +1108,9 @@ def paged_attention_prefill_biased(q: torch.Tensor, out: torch.Tensor, out_off: 
         raise KernelError("q must be [T, heads*head_dim] and cache [pages, 2, kv_heads, page_size, head_dim]")
     if dist_bias_t is not None and (dist_bias_t.dtype != torch.float32 or dist_bias_t.dim() != 2 or dist_bias_t.shape[0] != nq):
         raise KernelError("dist_bias_t must be float32 [heads, distances]")
+    dist_len = 0 if dist_bias_t is None else (-1 if analytic_bias else dist_bias_t.shape[1])
+    if analytic_bias and (dist_bias_t is None or dist_bias_t.shape[1] != 3):
+        raise KernelError("an analytic bias comes as float32 [heads, 3]: temperature, r1, r2")
     if head_gate is not None and (head_gate.dtype != torch.float32 or head_gate.stride(1) != 1):
         raise KernelError("head_gate must be float32 with unit stride along rows")
     f = _fn("attention_prefill", "llm_paged_attention_prefill_ex",
@@ -1111,7 +1120,7 @@ def paged_attention_prefill_biased(q: torch.Tensor, out: torch.Tensor, out_off: 
     _check(f(_ptr(q), _ptr(out), _ptr(cache), _ptr(tiles), n_tiles, _ptr(entry_slot), _ptr(entry_q_start),
              _ptr(entry_q_len), _ptr(entry_kv_len), _ptr(block_table), block_table.shape[1], nq, nkv, d,
              page_size, int(window) if window else 0, float(scale), cache.shape[0], _ptr(status), _ptr(dist_bias_t),
-             dist_bias_t.shape[1] if dist_bias_t is not None else 0, _ptr(head_gate),
+             dist_len, _ptr(head_gate),
              head_gate.stride(0) if head_gate is not None else 0, gate_off, float(out_scale), out.stride(0), out_off,
              _stream()), "paged_attention_prefill_biased")
     return out

@@ -283,11 +283,14 @@ class GatedAttentionMixer(BranchMixer):
                        and ops.fast_attention_supported(self.d, self.nq // self.nkv))
         # with a bias by distance or a gate per head: prompt portions still take a tensor-core kernel (the
         # mma.sync one, which adds the bias to its scores and gates as it stores), single tokens the general one
-        self._tuned_prompt = (not self._tuned and not scored and compute_dtype == torch.bfloat16 and self.dv == self.d
+        if scored and spec.distance_bias is not None:
+            raise ValueError("a distance table and a logarithmic distance bias or head temperature exclude one another")
+        self._tuned_prompt = (not self._tuned and compute_dtype == torch.bfloat16 and self.dv == self.d
                               and self.device.type == "cuda" and (self.gate_per_head or not spec.output_gate)
                               and ops.prefill_attention_supported(self.d))
         self._tuned_decode = self._tuned_prompt and ops.fast_attention_supported(self.d, self.nq // self.nkv)
         self.dist_table_t = None
+        self.analytic = False                   # dist_table_t holds (temperature, r1, r2) per head instead of a table
 
     def parameters(self) -> Dict[str, ParamSpec]:
         n, s = self.names, self.spec
@@ -325,6 +328,13 @@ class GatedAttentionMixer(BranchMixer):
             self.head_temp = t[n["temp"]].float().contiguous()
         if s.log_distance_bias:
             self.log_r1, self.log_r2 = t[n["r1"]].float().contiguous(), t[n["r2"]].float().contiguous()
+        if s.head_temperature or s.log_distance_bias:
+            # for the tensor-core kernels: (temperature, r1, r2) per head; they evaluate the bias themselves
+            one = torch.ones(self.nq, dtype=torch.float32, device=self.w_in.device)
+            self.dist_table_t = torch.stack([self.head_temp if self.head_temp is not None else one,
+                                             self.log_r1 if self.log_r1 is not None else one * 0,
+                                             self.log_r2 if self.log_r2 is not None else one * 0], dim=1).contiguous()
+            self.analytic = True
         if s.distance_bias is not None:
             rel = t[n["rel"]].float()
             rows, far = rel.shape[0], float(s.distance_bias[1])
@@ -392,7 +402,7 @@ class GatedAttentionMixer(BranchMixer):
                     q, out, out_col0, ctx.cache, work.padded_tiles if padded else work.prefill_tiles, n_tiles, b.entry_slot,
                     b.entry_q_start, b.entry_q_len, b.entry_kv_len, ctx.block_table, self.nq, self.nkv, self.d, ctx.page_size,
                     s.window, self.scale, ctx.status, dist_bias_t=self.dist_table_t, head_gate=gate,
-                    gate_off=col0 + self.g_off, out_scale=out_scale)
+                    gate_off=col0 + self.g_off, out_scale=out_scale, analytic_bias=self.analytic)
             if not n_dec:
                 return
             rows = work.padded_rows if padded else (None if n_dec == b.num_tokens else work.decode_rows)
@@ -401,7 +411,7 @@ class GatedAttentionMixer(BranchMixer):
                 splits = decode_key_splits(q.device, n_dec, self.nkv, self._decode_reach(b))
                 ops.paged_attention_decode(q, a, ctx.cache, rows, n_dec, b.positions, b.token_entry, b.entry_slot,
                                            ctx.block_table, self.nq, self.nkv, self.d, ctx.page_size, s.window, self.scale, splits,
-                                           ctx.status, dist_bias_t=self.dist_table_t)
+                                           ctx.status, dist_bias_t=self.dist_table_t, analytic_bias=self.analytic)
                 ops.gate_mul(a, gate, col0 + self.g_off, out, out_col0, s.output_gate, out_scale,
                              per_head=self.dv if self.gate_per_head else 0)
                 return

@@ -274,7 +274,7 @@ def test_window_edges(dtype, window):
 def test_attention_refuses_sizes_it_was_not_written_for():
     from litellmengine_b200.csrc.ops import KernelError
     z = lambda *a: torch.tensor(a, dtype=torch.int32, device=DEV)
-    for nq, nkv, d in ((4, 3, 32), (2, 1, 24), (2, 1, 272)):
+    for nq, nkv, d in ((4, 3, 32), (2, 1, 24), (2, 1, 528)):        # value widths above 512 have no instantiation
         with pytest.raises(KernelError, match="refused"):
             ops().paged_attention_generic(torch.zeros(1, nq * d, device=DEV), torch.zeros(1, 2, nkv, 4, d, device=DEV),
                                           z(0), z(0), z(0), z(0).view(1, 1), nq, nkv, d, 4, None, 1.0, status())

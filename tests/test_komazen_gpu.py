@@ -312,6 +312,52 @@ def test_attention_with_head_temperature_and_logarithmic_distance_bias():
     assert (flat[650] - pk.biased_attention_core(q, k, v, scale, temp, r1, r2)[650]).abs().max() > 0.1
 
 
+@pytest.mark.parametrize("d,group", [(64, 2), (128, 1), (128, 4)])
+def test_tensor_core_attention_with_temperature_and_logarithmic_bias(d, group):
+    """The kernels that a bfloat16 run takes at head sizes 64 and 128: a prompt portion that starts in the middle of a
+    page with keys before it, and single tokens in the split-key decode kernel; the temperature and the bias are
+    evaluated inside them from three numbers per head.  Keys that would win are placed far back."""
+    ops = _ops()
+    N, past, page, G, scale = 420, 37, 16, 2, 0.2
+    H, T = G * group, N - past
+    g = torch.Generator().manual_seed(d + group)
+    q, k, v = (torch.randn(N, n, d, generator=g, dtype=F64) for n in (H, G, G))
+    temp = 1 + 0.5 * torch.rand(H, generator=g, dtype=F64)
+    r1, r2 = 1 + 2 * torch.rand(H, generator=g, dtype=F64), 0.1 + 2 * torch.rand(H, generator=g, dtype=F64)
+    r1[0] = 0.0
+    for i, j in ((419, 0), (418, 15), (300, 16), (200, 3)):
+        k[j] = q[i, ::group] * (40.0 / d)          # a score of about ten: wins by far without the bias, loses with it
+    q, k, v = (t.to(torch.bfloat16).double() for t in (q, k, v))
+    ref = pk.biased_attention_core(q[past:], k, v, scale, temp, r1, r2, first_position=past)
+    order = np.random.RandomState(2).permutation(N // page + 6)[:-(-N // page)]
+    block_table = torch.full((3, len(order) + 2), -1, dtype=torch.int32)
+    block_table[1, :len(order)] = torch.as_tensor(order, dtype=torch.int32)
+    block_table = block_table.to(DEV)
+    cache = torch.zeros(N // page + 6, 2, G, page, d, dtype=torch.bfloat16, device=DEV)
+    for j in range(N):
+        cache[order[j // page], 0, :, j % page] = k[j].to(torch.bfloat16).to(DEV)
+        cache[order[j // page], 1, :, j % page] = v[j].to(torch.bfloat16).to(DEV)
+    qd = q[past:].reshape(T, -1).to(torch.bfloat16).to(DEV)
+    three = torch.stack([temp, r1, r2], dim=1).float().to(DEV).contiguous()
+    out = torch.zeros(T, H * d, dtype=torch.bfloat16, device=DEV)
+    status = torch.zeros(2, dtype=torch.int32, device=DEV)
+    tiles = _i32([(0, r0) for r0 in range(0, T, ops.PREFILL_TILE_ROWS)])
+    ops.paged_attention_prefill_biased(qd, out, 0, cache, tiles, tiles.shape[0], _i32([1]), _i32([0]), _i32([T]), _i32([N]),
+                                       block_table, H, G, d, page, None, scale, status, dist_bias_t=three, analytic_bias=True)
+    assert status.tolist() == [0, 0]
+    assert (out.double().cpu().view(T, H, d) - ref).abs().max() < 0.06
+    if ops.fast_attention_supported(d, group):
+        for splits in (1, 3):
+            a = torch.zeros(T, H * d, dtype=torch.bfloat16, device=DEV)
+            picked = [T - 1, T - 2, 5, 263]
+            ops.paged_attention_decode(qd, a, cache, _i32(picked + [-1]), 5, _i32(list(range(past, N))), _i32([0] * T), _i32([1]),
+                                       block_table, H, G, d, page, None, scale, splits, status, dist_bias_t=three, analytic_bias=True)
+            assert status.tolist() == [0, 0]
+            assert (a.double().cpu().view(T, H, d)[picked] - ref[picked]).abs().max() < 0.06, splits
+    flat = pk.biased_attention_core(q[past:], k, v, scale, temp, r1 * 0, r2, first_position=past)
+    assert (flat[T - 1] - ref[T - 1]).abs().max() > 0.1           # the bias decides what the last query sees
+
+
 @pytest.mark.parametrize("window,dims", [(None, 8), (1, 8), (7, 4), (64, 8), (65, 0)])
 def test_latent_attention_kernels_window_edges_and_rotation(window, dims):
     """The kernels between the projections of a latent attention layer, on projections given as numbers: latents
