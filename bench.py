@@ -2,7 +2,7 @@
 """Benchmark of the engine on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers L]
-                    [--impl ours|reference] [--points LIST | --no-points] [--design tobovik|gubidra [--sizes LIST]]
+                    [--impl ours|reference] [--points LIST | --no-points] [--design tobovik|gubidra|komazen [--sizes LIST]]
 
 Headline (`value`): decode tokens/s of `batch` requests whose context ends at 4,096 tokens, on a
 model with the layer sizes of Qwen3-8B (36 layers unless --layers says fewer; the JSON names both
@@ -20,7 +20,8 @@ the Qwen3-32B shape at batch 16 (each sub-record names its sizes).
 `--design tobovik [--sizes w1024,w2048,w4096]` measures something else and prints a line of its own:
 prefill and decode of the Tobovik design beside Qwen3 at equal width, heads, feed-forward, depth and
 vocabulary, and the design's own kernels beside the like kernels of the Qwen3 path with their roofline
-fractions.  `--design gubidra` does the same for the Gubidra design beside Tobovik, its closest model.
+fractions.  `--design gubidra` does the same for the Gubidra design beside Tobovik, its closest model, and
+`--design komazen` for the Komazen design beside Qwen3.
 Without it the workload and the line above are what they always were.
 
 `--impl reference` times the unmodified reference engine (float32, its only precision) on the same
@@ -565,6 +566,155 @@ def gubidra_dict(width, ff, heads, kv, layers):
             "embedding": {"scale": 1.0}, "streams": 2, "layers": [(ret, ret, att, mem)[i % 4] for i in range(layers)]}
 
 
+def komazen_dict(width, ff, heads, kv, layers):
+    """Attention (head temperature, logarithmic distance bias), latent attention that keeps its own rows, attention,
+    latent attention that reads the rows of the latent layer before it, and so on; heads of 128; latents of 512 with a
+    rotated part of 64 (one cached row of 576 per token), a query latent of three eighths of the width, a window of
+    1,024 keys; three convolution taps; the dense gated feed-forward of equal size."""
+    mlp = {"kind": "dense", "ff": ff}
+    att = {"type": "attention", "mlp": mlp, "mixer": {"heads": heads, "kv_heads": kv, "dim": DESIGN_HEAD, "vdim": DESIGN_HEAD,
+                                                      "scale": DESIGN_HEAD ** -0.5}}
+
+    def lat(src):
+        m = {"heads": heads, "dim": DESIGN_HEAD, "rot_dim": 64, "vdim": DESIGN_HEAD, "q_rank": 3 * width // 8, "kv_rank": 512,
+             "scale": (DESIGN_HEAD + 64) ** -0.5, "rot": {"base": 10000.0, "dims": 64}, "mask": {"size": 1024}}
+        if src is not None:
+            m["kv_from"] = src
+        return {"type": "latent_attention", "mlp": mlp, "mixer": m}
+    return {"architecture": "Komazen", "vocab": DESIGN_VOCAB, "width": width, "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0},
+            "postln_alpha": 2.0, "canon": {"taps": 3},
+            "layers": [att if i % 2 == 0 else lat(i - 2 if i % 4 == 3 else None) for i in range(layers)]}
+
+
+def komazen_bench(args, pk, measure) -> int:
+    """`--design komazen`: the design beside Qwen3 (the closest model: softmax attention and a dense gated feed-forward
+    in every layer) at equal width, heads, feed-forward, depth and vocabulary, and its kernels beside their like."""
+    import torch
+    from litellmengine_b200.config import config_from_dict
+    from litellmengine_b200.csrc import ops
+    from litellmengine_b200.csrc.microbench import Flusher, timed
+    import types
+    dev = "cuda:0"
+    sizes = {}
+    for name, (width, ff, heads, kv, layers) in DESIGN_SIZES.items():
+        if args.sizes and name not in args.sizes.split(","):
+            continue
+        qwen = dict(QWEN3_8B, num_hidden_layers=layers, hidden_size=width, num_attention_heads=heads, num_key_value_heads=kv,
+                    head_dim=DESIGN_HEAD, intermediate_size=ff, vocab_size=DESIGN_VOCAB)
+        sizes[name] = {"shape": {"width": width, "ff": ff, "heads": heads, "kv_heads": kv, "layers": layers, "vocab": DESIGN_VOCAB}}
+        for label, cfg in (("komazen", komazen_dict(width, ff, heads, kv, layers)), ("qwen3", qwen)):
+            sizes[name][label] = measure(config_from_dict(cfg))
+            gc.collect()
+            torch.cuda.empty_cache()
+        k, q = sizes[name]["komazen"], sizes[name]["qwen3"]
+        sizes[name]["komazen_over_qwen3"] = {x: round(k[x] / q[x], 3) for x in k if x.endswith("tok_s")}
+    flush = Flusher(dev)
+    width, ff, heads, kv, _ = DESIGN_SIZES["w4096"]
+    T, hbm, d = 2048, pk["hbm_gbs"] * 1e9, DESIGN_HEAD
+    tensor_peak = pk.get("bf16_tflops", 1590.0) * 1e12
+    kernels = {}
+
+    def add(name, fn, nbytes=None, flops=None):
+        sec = timed(fn, 5, 3, flush)
+        rec = {"us": round(sec * 1e6, 2)}
+        if nbytes is not None:
+            rec.update(gbs=round(nbytes / sec / 1e9, 1), frac_of_hbm=round(nbytes / sec / hbm, 4))
+        if flops is not None:
+            rec.update(tflops=round(flops / sec / 1e12, 2), frac_of_bf16_peak=round(flops / sec / tensor_peak, 4))
+        kernels[name] = rec
+
+    i32 = lambda x: torch.as_tensor(x, dtype=torch.int32, device=dev)
+    pos = torch.arange(T, device=dev, dtype=torch.int32)
+    prompt = types.SimpleNamespace(positions=pos, token_entry=i32([0] * T), entry_slot=i32([0]), entry_q_start=i32([0]),
+                                   entry_q_len=i32([T]))
+    h, y, w = torch.randn(T, width, device=dev), torch.randn(T, width, device=dev), torch.ones(width, device=dev)
+    taps = torch.randn(width, 3, device=dev) * 0.3
+    kept = torch.zeros(1, 2, width, device=dev)
+    add("short_conv (new: the stream plus its 3-tap causal convolution, stored in bfloat16)",
+        lambda: ops.short_conv(h, taps, kept, prompt, torch.bfloat16), nbytes=T * width * (4 + 2))
+    add("scaled_add_norm (new: norm after the sum, keeps the convolution's rows)",
+        lambda: ops.scaled_add_norm(h, y, w, 2.0, 1e-5, kept, prompt), nbytes=T * width * (4 + 4 + 4))
+    add("rmsnorm (like: residual add + norm, bfloat16 copy)", lambda: ops.rmsnorm(h, w, 1e-5, torch.bfloat16, delta=y, write_sum=True),
+        nbytes=T * width * (4 + 4 + 4 + 2))
+    gu = torch.randn(T, 2 * ff, device=dev).to(torch.bfloat16)
+    add("gelu_tanh gate (new)", lambda: ops.silu_and_mul(gu, activation="gelu_tanh"), nbytes=T * ff * 6)
+    add("silu gate (like)", lambda: ops.silu_and_mul(gu), nbytes=T * ff * 6)
+    # the latent layer's small kernels
+    Q, R, P = 3 * width // 8, 512, 64
+    pages = T // PAGE
+    status = torch.zeros(2, dtype=torch.int32, device=dev)
+    proj = torch.randn(T, Q + R + P, device=dev)
+    rows = torch.zeros(pages, 1, PAGE, R + P, device=dev, dtype=torch.bfloat16)
+    tbl = torch.arange(pages, device=dev, dtype=torch.int32).view(1, pages)
+    invf = torch.pow(torch.tensor(1e4), -torch.arange(0, P, 2, dtype=torch.float32) / P).to(dev)
+    ones_q, ones_r = torch.ones(Q, device=dev), torch.ones(R, device=dev)
+    add("latent_prepare (new: two latent norms, rotation, page write)",
+        lambda: ops.latent_prepare(proj, 0, Q, Q, R, P, P, ones_q, ones_r, 1e-5, invf, rows, prompt, tbl, PAGE, status, torch.bfloat16),
+        nbytes=T * (Q + R + P) * (4 + 2))
+    q32 = torch.randn(T, heads * (d + P), device=dev)
+    add("latent_q_split (new: query rotation, head-major copy)",
+        lambda: ops.latent_q_split(q32, pos, invf, heads, d, P, R, P, torch.bfloat16), nbytes=T * heads * (d + P) * (4 + 2))
+    qkv = torch.randn(T, (heads + 2 * kv) * d, device=dev)
+    cache = torch.zeros(pages, 2, kv, PAGE, d, device=dev, dtype=torch.bfloat16)
+    hw = torch.ones(d, device=dev)
+    invd = torch.pow(torch.tensor(1e6), -torch.arange(0, d, 2, dtype=torch.float32) / d).to(dev)
+    add("qk_norm_rope_kv_write (like: head norm, rotation, page write)",
+        lambda: ops.qk_norm_rope_kv_write(qkv, cache, pos, prompt.token_entry, prompt.entry_slot, tbl, hw, hw, 1e-6, invd, d, heads, kv,
+                                          d, PAGE, True, status, q_dtype=torch.bfloat16), nbytes=T * (heads + 2 * kv) * d * (4 + 2))
+    # attention with temperature and logarithmic bias beside the plain kernels: one 2,048-token prompt, 64 single tokens
+    cache.normal_()
+    qa = torch.randn(T, heads * d, device=dev).to(torch.bfloat16)
+    oa = torch.empty_like(qa)
+    three = torch.stack([torch.ones(heads), torch.ones(heads), torch.ones(heads)], dim=1).to(dev).contiguous()
+    tiles = torch.tensor([(0, r0) for r0 in range(0, T, ops.PREFILL_TILE_ROWS)][::-1], device=dev, dtype=torch.int32)
+    e_len = i32([T])
+    attn_flops = 4.0 * heads * d * (T * (T + 1) / 2)
+    common = (cache, tiles, tiles.shape[0], prompt.entry_slot, prompt.entry_q_start, e_len, e_len, tbl, heads, kv, d, PAGE, None,
+              d ** -0.5, status)
+    add("prompt attention with temperature + logarithmic bias (new; mma.sync): 2048 tokens",
+        lambda: ops.paged_attention_prefill_biased(qa, oa, 0, *common, dist_bias_t=three, analytic_bias=True), flops=attn_flops)
+    add("prompt attention, the same mma.sync kernel without them (like)", lambda: ops.paged_attention_prefill(qa, oa, *common),
+        flops=attn_flops)
+    if ops.prefill_tcgen05_supported(d, PAGE):
+        add("prompt attention, the tcgen05 kernel (like: what the closest model's prompt portions take)",
+            lambda: ops.paged_attention_prefill_tcgen05(qa, oa, *common), flops=attn_flops)
+    Bd, ctx = 64, 1024
+    dpages = ctx // PAGE
+    dcache = torch.randn(Bd * dpages, 2, kv, PAGE, d, device=dev).to(torch.bfloat16)
+    dtbl = torch.arange(Bd * dpages, device=dev, dtype=torch.int32).view(Bd, dpages)
+    dpos = torch.full((Bd,), ctx - 1, device=dev, dtype=torch.int32)
+    dent = torch.arange(Bd, device=dev, dtype=torch.int32)
+    kv_bytes = Bd * ctx * 2 * kv * d * 2
+    add(f"decode attention with temperature + logarithmic bias, split-key kernel (new): {Bd} tokens, {ctx} keys each",
+        lambda: ops.paged_attention_decode(qa[:Bd], oa[:Bd], dcache, None, Bd, dpos, dent, dent, dtbl, heads, kv, d, PAGE, None, d ** -0.5,
+                                           2, status, dist_bias_t=three, analytic_bias=True), nbytes=kv_bytes)
+    add("decode attention, split-key kernel (like)",
+        lambda: ops.paged_attention_decode(qa[:Bd], oa[:Bd], dcache, None, Bd, dpos, dent, dent, dtbl, heads, kv, d, PAGE, None, d ** -0.5,
+                                           2, status), nbytes=kv_bytes)
+    # latent attention over the cached rows: every head of a token reads the same rows
+    lrows = torch.randn(Bd * dpages, 1, PAGE, R + P, device=dev).to(torch.bfloat16)
+    ql = torch.randn(T, heads * (R + P), device=dev).to(torch.bfloat16)
+    ol = torch.empty(T, heads * R, device=dev, dtype=torch.bfloat16)
+    lat_bytes = Bd * ctx * (R + P) * 2
+    lat_flops = 2.0 * heads * (2 * R + P)
+
+    def latent(n_tok, positions, entries, slots, table, window):
+        return lambda: ops.latent_attention(ql[:n_tok], lrows, positions, entries, slots, table, heads, R, P, PAGE, window, 0.07, status,
+                                            ol[:n_tok])
+    add(f"latent attention, {Bd} single tokens, {ctx} rows each (new)", latent(Bd, dpos, dent, dent, dtbl, 1024),
+        nbytes=lat_bytes, flops=lat_flops * Bd * ctx)
+    ptbl = torch.arange(pages, device=dev, dtype=torch.int32).view(1, pages)
+    walked = sum(min(p + 1, 1024) for p in range(T))
+    add("latent attention, one 2048-token prompt, window 1024 (new)",
+        latent(T, pos, prompt.token_entry, prompt.entry_slot, ptbl, 1024), flops=lat_flops * walked)
+    print(json.dumps({"metric": "tokens/s of the Komazen design beside Qwen3 at equal sizes (bfloat16, random weights)",
+                      "design": "komazen", "prompt_tokens": 2048, "decode_context": 1024, "steps": args.steps,
+                      "warmup": args.warmup, "sizes": sizes, "kernels_at_w4096": kernels,
+                      "peaks": {"hbm_gbs": pk["hbm_gbs"], "bf16_tflops": round(tensor_peak / 1e12, 1), "source": pk["source"]},
+                      "l2": "kernel timings: a 256 MB buffer is overwritten between launches; steps read every weight"}))
+    return 0
+
+
 def gubidra_bench(args, pk, measure) -> int:
     """`--design gubidra`: the design beside Tobovik (the closest model: softmax attention beside a linear
     recurrence) at equal width, heads, feed-forward, depth and vocabulary, and its kernels beside their like."""
@@ -807,7 +957,7 @@ def design_bench(args, pk) -> int:
             b.record()
             torch.cuda.synchronize()
             ms = a.elapsed_time(b) / steps
-            state = sum(t[0].numel() * t.element_size() for k, t in runner.cache.state.items() if isinstance(k, int))
+            state = sum(t[0].numel() * t.element_size() for k, t in runner.cache.state.items() if not isinstance(k, str))
             step_bytes = runner.model.weight_bytes() + B * (runner.cache.bytes_per_token() * (context - steps // 2) + 2 * state)
             rec[f"decode_b{B}_ms"] = round(ms, 4)
             rec[f"decode_b{B}_tok_s"] = round(B / (ms * 1e-3), 1)
@@ -820,6 +970,8 @@ def design_bench(args, pk) -> int:
 
     if args.design == "gubidra":
         return gubidra_bench(args, pk, measure)
+    if args.design == "komazen":
+        return komazen_bench(args, pk, measure)
     sizes = {}
     for name, (width, ff, heads, kv, layers) in DESIGN_SIZES.items():
         if args.sizes and name not in args.sizes.split(","):
@@ -939,9 +1091,9 @@ def main() -> int:
     ap.add_argument("--points", default=",".join(ALL_POINTS),
                     help="which extra measurements to take: " + ",".join(ALL_POINTS))
     ap.add_argument("--no-points", action="store_true", help="the headline, prefill and e2e only")
-    ap.add_argument("--design", choices=["tobovik", "gubidra"],
-                    help="instead of the default workload: this design beside its closest model (tobovik beside Qwen3, "
-                         "gubidra beside tobovik) at equal sizes, and its kernels")
+    ap.add_argument("--design", choices=["tobovik", "gubidra", "komazen"],
+                    help="instead of the default workload: this design beside its closest model (tobovik and komazen beside "
+                         "Qwen3, gubidra beside tobovik) at equal sizes, and its kernels")
     ap.add_argument("--sizes", default="", help="with --design: which of " + ",".join(DESIGN_SIZES) + " (default: all)")
     args = ap.parse_args()
 

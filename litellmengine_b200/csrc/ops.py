@@ -661,6 +661,42 @@ def latent_q_split(q: torch.Tensor, positions: torch.Tensor, inv_freq: Optional[
     return qn, packed
 
 
+def latent_attention_supported(R: int, P: int) -> bool:
+    """Whether the tensor-core kernel over cached latent rows takes a latent of R and a rotated part of P entries."""
+    return bool(_fn("latent_attention", "llm_latent_attention_supported", [c_int, c_int])(R, P))
+
+
+def latent_attention(q: torch.Tensor, rows_cache: torch.Tensor, positions, token_entry, entry_slot,
+                     block_table: torch.Tensor, H: int, R: int, P: int, page_size: int, window: Optional[int], scale: float,
+                     status: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """Causal softmax attention of the packed queries q (bfloat16 [T, H * (R + P)]) over each token's pages of
+    `rows_cache` (bfloat16 [pages, 1, page, R + P]): the scores run over all R + P entries of a row, the values are
+    its first R entries.  `window`: a token sees itself and the window - 1 rows before it (None: all).  Writes the
+    weighted latent sums into `out` (bfloat16 [T, H * R])."""
+    _dev(q, rows_cache, positions, token_entry, entry_slot, block_table, status, out)
+    T, DK = q.shape[0], R + P
+    if q.dtype != torch.bfloat16 or rows_cache.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+        raise KernelError("latent_attention runs in bfloat16")
+    if q.dim() != 2 or q.shape[1] != H * DK or not q.is_contiguous() or tuple(out.shape) != (T, H * R) or not out.is_contiguous():
+        raise KernelError("q must be a dense [T, heads * (R + P)] and out a dense [T, heads * R]")
+    if (rows_cache.dim() != 4 or tuple(rows_cache.shape[1:]) != (1, page_size, DK)
+            or rows_cache[0].stride() != (page_size * DK, DK, 1)):
+        raise KernelError("rows_cache must be [pages, 1, page_size, R + P] with dense pages")
+    splits = _fn("latent_attention", "llm_latent_attention_splits", [c_int, c_int, c_int, c_int, c_int])(
+        T, H, int(window or 0), block_table.shape[1], page_size)
+    part_acc = part_ml = None
+    if splits > 1:          # few tokens: a token's rows are dealt to several CTAs, whose sums a second kernel merges
+        part_acc = torch.empty((T, splits, H, R), dtype=torch.float32, device=q.device)
+        part_ml = torch.empty((T, splits, H, 2), dtype=torch.float32, device=q.device)
+    f = _fn("latent_attention", "llm_latent_attention",
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+             c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p])
+    _check(f(_ptr(q), _ptr(out), _ptr(part_acc), _ptr(part_ml), splits, _ptr(rows_cache), rows_cache.stride(0), _ptr(positions),
+             _ptr(token_entry), _ptr(entry_slot), _ptr(block_table), block_table.shape[1], T, H, R, P, page_size,
+             int(window or 0), float(scale), rows_cache.shape[0], _ptr(status), _stream()), "latent_attention")
+    return out
+
+
 # ---- gated linear attention ------------------------------------------------------------------
 GLA_FULL, GLA_LOCAL, GLA_OUT = 0, 1, 2
 

@@ -34,7 +34,8 @@ class LatentAttentionMixer:
 
     One product yields [dq | dkv | g] per token in float32; `latent_prepare` norms both latents, rotates kr and
     writes the page row; W_uq; `latent_q_split` rotates qr and lays qn out head-major; a batched product with
-    W_uk^T fills q_abs; attention; a batched product with W_uv^T; the gate; W_o."""
+    W_uk^T fills q_abs; attention (bfloat16: the tensor-core kernel in which all heads of a token share each staged
+    tile of rows; float32: the general kernel); a batched product with W_uv^T; the gate; W_o."""
 
     graph_safe = True           # kernels and library products on the current stream only
     any_division_safe = True    # nothing is shaped by the number of entries
@@ -70,6 +71,9 @@ class LatentAttentionMixer:
         self.dkv_off = self.Q
         self.g_off = self.Q + (self.R + self.P if spec.has_kv else 0)
         self.gate_width = self.H * self.V if spec.output_gate else 0
+        # bfloat16 on the tensor-core kernel over the cached rows; float32 (and other latent sizes) on the general kernel
+        self.tensor_core = (compute_dtype == torch.bfloat16 and self.device.type == "cuda"
+                            and ops.latent_attention_supported(self.R, self.P))
         self.w_in = self.w_uq = self.w_uk_t = self.w_uv_t = self.w_o = None
         self.wq_norm = self.wkv_norm = None
 
@@ -122,9 +126,13 @@ class LatentAttentionMixer:
         torch.bmm(qn, self.w_uk_t if self.w_uk_t.dtype == qn.dtype else self.w_uk_t.to(qn.dtype),
                   out=packed.view(T, H, R + P)[:, :, :R].permute(1, 0, 2))
         lat = torch.empty((T, H * R), dtype=self.dtype, device=x.device)
-        ops.paged_attention_generic_kv(packed, ctx.cache_keys, None, b.positions, b.token_entry, b.entry_slot,
-                                       ctx.block_table, H, 1, R + P, R, ctx.page_size, s.window, self.scale, ctx.status, lat,
-                                       values_in_keys=True)
+        if self.tensor_core:
+            ops.latent_attention(packed, ctx.cache_keys, b.positions, b.token_entry, b.entry_slot, ctx.block_table, H, R, P,
+                                 ctx.page_size, s.window, self.scale, ctx.status, lat)
+        else:
+            ops.paged_attention_generic_kv(packed, ctx.cache_keys, None, b.positions, b.token_entry, b.entry_slot,
+                                           ctx.block_table, H, 1, R + P, R, ctx.page_size, s.window, self.scale, ctx.status,
+                                           lat, values_in_keys=True)
         heads = torch.empty((T, H * V), dtype=self.dtype, device=x.device)
         torch.bmm(lat.view(T, H, R).permute(1, 0, 2), self.w_uv_t if self.w_uv_t.dtype == lat.dtype else self.w_uv_t.to(lat.dtype),
                   out=heads.view(T, H, V).permute(1, 0, 2))

@@ -73,6 +73,16 @@ KOMA_D = _config(89, 36, 1e-6, 0.5, 1.0, 2, [
 ])
 KOMA_D_PAGE = 8
 
+# E: latent ranks of 64 and 128, which the bfloat16 run takes on the tensor-core kernel over the cached rows: more heads
+# than half a block of heads, a reader of other head sizes, a window that ends in the middle of a tile of rows
+KOMA_E = _config(97, 72, 1e-5, 2.0, 1.5, 3, [
+    _layer("latent_attention", _latent(18, 8, 32, 12, 36, 64, 0.2, 50, 3000.0), 80),
+    _layer("attention", _attn(3, 1, 16, 24, 0.25), 64),
+    _layer("latent_attention", _latent(5, 24, 32, 16, 28, 64, 0.15, 77, 3000.0, kv_from=0), 80),
+    _layer("latent_attention", _latent(2, 16, 16, 40, 24, 128, 0.2, 0, 700.0), None),
+])
+KOMA_E_PAGE = 32
+
 
 def tensor_shapes(cfg: dict) -> Dict[str, tuple]:
     """Names and shapes of a model's tensors, written out from the design's naming rules."""

@@ -28,7 +28,7 @@ def test_plan_of_a_configuration():
 
 
 def test_tensors_are_the_design_s_names():
-    for cfg in (km.KOMA_A, km.KOMA_B, km.KOMA_C, km.KOMA_D):
+    for cfg in (km.KOMA_A, km.KOMA_B, km.KOMA_C, km.KOMA_D, km.KOMA_E):
         want = km.tensor_shapes(cfg)
         got = model_parameters(config_from_dict(cfg).plan())
         assert {n: tuple(p.shape) for n, p in got.items()} == want

@@ -17,7 +17,7 @@ DEV = "cuda:0"
 F64 = torch.float64
 
 CASES = {"A": (km.KOMA_A, km.KOMA_A_PAGE, 3), "B": (km.KOMA_B, km.KOMA_B_PAGE, 5), "C": (km.KOMA_C, km.KOMA_C_PAGE, 9),
-         "D": (km.KOMA_D, km.KOMA_D_PAGE, 11)}
+         "D": (km.KOMA_D, km.KOMA_D_PAGE, 11), "E": (km.KOMA_E, km.KOMA_E_PAGE, 13)}
 # root mean square over the vocabulary of (difference minus its mean), as a fraction of the reference logits'
 # spread; the float32 run is measured against the plain code in double precision
 LIMIT = {"float32": 1e-4, "bfloat16": 0.12}
@@ -78,7 +78,7 @@ def requests(cfg, lengths, seed):
 
 # ---- whole models, every cutting ------------------------------------------------------------------
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("case", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("case", ["A", "B", "C", "D", "E"])
 def test_every_cutting_matches_plain(case, dtype):
     cfg, page, w = model_of(case)
     reqs = requests(cfg, [1, 2, 3, 37, 90, 150], seed=1)
@@ -420,6 +420,77 @@ def test_latent_attention_kernels_window_edges_and_rotation(window, dims):
         window += 1
         wider, _ = plain(dkv)
         assert (wide[148] - wider[148]).abs().max() > 0.05
+
+
+@pytest.mark.parametrize("H,R,P,window,page", [(3, 64, 16, 40, 16), (16, 64, 0, None, 64), (17, 128, 32, 33, 16),
+                                                 (40, 64, 48, 32, 32), (6, 256, 16, 97, 64), (33, 512, 64, 64, 16)])
+def test_tensor_core_latent_attention_over_cached_rows(H, R, P, window, page):
+    """The bfloat16 kernel in which all heads of a token share the staged rows, alone, on packed queries and cached
+    rows given as numbers: a prompt portion that starts in the middle of a page beside single decoded tokens of two
+    other requests, pages scattered over the pool, head counts that fill no, one and more than one block of heads.
+    For some queries one row is turned towards head 0 so that it would win by far, and sits just inside or just outside
+    the window, at a page's last and first place, at the sequence's first token and hundreds of rows back."""
+    ops = _ops()
+    if not ops.latent_attention_supported(R, P):
+        pytest.skip("not a size of the kernel")
+    g = torch.Generator().manual_seed(H * 1000 + R + P)
+    DK, scale = R + P, 0.9 * (R + P) ** -0.5
+    lengths = {0: 333, 1: 70, 2: 1}                         # rows cached per slot, the step's tokens included
+    n_pages = {s: -(-n // page) for s, n in lengths.items()}
+    pool = sum(n_pages.values()) + 4
+    order = np.random.RandomState(R + H).permutation(pool)
+    table = torch.full((3, max(n_pages.values()) + 1), -1, dtype=torch.int32)
+    rows, at = {}, 0
+    for s, n in lengths.items():
+        table[s, :n_pages[s]] = torch.as_tensor(order[at:at + n_pages[s]], dtype=torch.int32)
+        at += n_pages[s]
+        rows[s] = bf16_exact(torch.randn(n, DK, generator=g, dtype=F64))
+    portions = [(0, 333 - 150, 150), (1, 69, 1), (2, 0, 1)]
+    b = _batch(portions)
+    T = b.num_tokens
+    q = bf16_exact(torch.randn(T, H, DK, generator=g, dtype=F64))
+    w = window or 10 ** 6
+    # (token of the portion in slot 0, how far back the row sits that head 0 is drawn to)
+    first = 333 - 150
+    for tok, back in ((149, w - 1 if window else 320), (148, w if window else 300), (120, 0), (100, (first + 100) % page),
+                      (99, (first + 99) % page + 1), (60, first + 60)):
+        j = first + tok - back
+        if 0 <= j:
+            rows[0][j] = bf16_exact(q[tok, 0] * 12.0 / scale / q[tok, 0].pow(2).sum())
+    cache = torch.zeros(pool, 1, page, DK, dtype=torch.bfloat16, device=DEV)
+    for s, n in lengths.items():
+        for j in range(n):
+            cache[int(table[s, j // page]), 0, j % page] = rows[s][j].to(torch.bfloat16)
+    ref = torch.zeros(T, H, R, dtype=F64)
+    t = 0
+    for slot, p0, n in portions:
+        kv = rows[slot][:p0 + n]
+        sc = torch.einsum("thd,sd->hts", q[t:t + n], kv) * scale
+        i, j = torch.arange(p0, p0 + n)[:, None], torch.arange(p0 + n)[None, :]
+        vis = (j <= i) & (i - j < w)
+        ref[t:t + n] = pk.softmax_core(sc, kv[None, :, :R].expand(H, -1, -1), vis).permute(1, 0, 2)
+        t += n
+    out = torch.full((T, H * R), 7.0, dtype=torch.bfloat16, device=DEV)
+    status = torch.zeros(2, dtype=torch.int32, device=DEV)
+    ops.latent_attention(q.reshape(T, H * DK).to(torch.bfloat16).to(DEV), cache, b.positions, b.token_entry, b.entry_slot,
+                         table.to(DEV), H, R, P, page, window, scale, status, out)
+    assert status.tolist() == [0, 0]
+    err = ((out.double().cpu().view(T, H, R) - ref).abs() / (1.0 + ref.abs())).max()
+    assert err < 0.02, (H, R, P, window, page, float(err))
+    # the last token of every request alone, as in decoding: each token's rows are dealt to several CTAs and merged
+    b1 = _batch([(0, 332, 1), (1, 69, 1), (2, 0, 1)])
+    out1 = torch.full((3, H * R), 7.0, dtype=torch.bfloat16, device=DEV)
+    ops.latent_attention(q[149:].reshape(3, H * DK).to(torch.bfloat16).to(DEV), cache, b1.positions, b1.token_entry, b1.entry_slot,
+                         table.to(DEV), H, R, P, page, window, scale, status, out1)
+    assert status.tolist() == [0, 0]
+    err = ((out1.double().cpu().view(3, H, R) - ref[149:]).abs() / (1.0 + ref[149:].abs())).max()
+    assert err < 0.02, ("single tokens", H, R, P, window, page, float(err))
+    if window:                                              # the row just outside the window must not be seen
+        assert (ref[148, 0] - rows[0][333 - 150 + 148 - w][:R]).abs().max() > 0.5
+
+
+def bf16_exact(x):
+    return x.to(torch.bfloat16).to(x.dtype)
 
 
 def test_gelu_gate_activation():
