@@ -21,6 +21,17 @@
 
 #define CN_THREADS 256
 
+template <int V>
+__device__ __forceinline__ void load_row(float (&v)[V], const float* p) {       // V == 4: one 16-byte load
+    if constexpr (V == 4) {
+        const float4 f = *reinterpret_cast<const float4*>(p);
+        v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
+    } else {
+#pragma unroll
+        for (int u = 0; u < V; ++u) v[u] = p[u];
+    }
+}
+
 template <typename TO, int V>
 __global__ void short_conv_kernel(
     const float* __restrict__ x, const float* __restrict__ w, TO* __restrict__ out, const float* __restrict__ kept,
@@ -35,22 +46,35 @@ __global__ void short_conv_kernel(
     const int R = taps - 1;
     const float* ring = kept ? kept + static_cast<size_t>(entry_slot[e]) * kept_slot_stride : nullptr;
     float acc[V], cur[V];
-#pragma unroll
-    for (int u = 0; u < V; ++u) cur[u] = x[static_cast<size_t>(t) * width + c + u];
+    load_row<V>(cur, x + static_cast<size_t>(t) * width + c);
 #pragma unroll
     for (int u = 0; u < V; ++u) acc[u] = cur[u];
-    for (int back = R; back >= 0; --back) {                 // oldest first: the order of additions is fixed
+    for (int back = R; back >= 1; --back) {                 // oldest first: the order of additions is fixed
         const int j = taps - 1 - back;
-        const float* src = nullptr;
-        if (back == 0) src = nullptr;
-        else if (t - back >= q0) src = x + static_cast<size_t>(t - back) * width + c;
+        const float* src;
+        if (t - back >= q0) src = x + static_cast<size_t>(t - back) * width + c;
         else if (pos - back >= 0 && ring) src = ring + static_cast<size_t>((pos - back) % R) * width + c;
         else continue;                                      // before the sequence's start: zero
+        float old[V];
+        load_row<V>(old, src);
 #pragma unroll
-        for (int u = 0; u < V; ++u) acc[u] += w[static_cast<size_t>(c + u) * taps + j] * (back == 0 ? cur[u] : src[u]);
+        for (int u = 0; u < V; ++u) acc[u] += w[static_cast<size_t>(c + u) * taps + j] * old[u];
     }
 #pragma unroll
-    for (int u = 0; u < V; ++u) out[static_cast<size_t>(t) * width + c + u] = from_f32<TO>(acc[u]);
+    for (int u = 0; u < V; ++u) acc[u] += w[static_cast<size_t>(c + u) * taps + taps - 1] * cur[u];
+    TO* o = out + static_cast<size_t>(t) * width + c;
+    if constexpr (V == 4 && sizeof(TO) == 4) {
+        *reinterpret_cast<float4*>(o) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    } else if constexpr (V == 4 && sizeof(TO) == 2) {
+        __nv_bfloat162 lo2 = __floats2bfloat162_rn(acc[0], acc[1]), hi2 = __floats2bfloat162_rn(acc[2], acc[3]);
+        uint2 pk;
+        pk.x = *reinterpret_cast<unsigned*>(&lo2);
+        pk.y = *reinterpret_cast<unsigned*>(&hi2);
+        *reinterpret_cast<uint2*>(o) = pk;
+    } else {
+#pragma unroll
+        for (int u = 0; u < V; ++u) o[u] = from_f32<TO>(acc[u]);
+    }
 }
 
 extern "C" int llm_short_conv(const float* x, const float* w, void* out, int out_dtype, const float* kept,
@@ -60,7 +84,7 @@ extern "C" int llm_short_conv(const float* x, const float* w, void* out, int out
     if (num_tokens <= 0) return LLM_OK;
     if (width <= 0 || taps < 1 || (taps > 1 && !kept)) return LLM_REFUSED_SIZE;
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-    const bool four = width % 4 == 0;
+    const bool four = width % 4 == 0 && aligned16(x) && aligned16(out) && (!kept || (aligned16(kept) && kept_slot_stride % 4 == 0));
     const int per = four ? 4 : 1;
     const dim3 grid(num_tokens, (width + CN_THREADS * per - 1) / (CN_THREADS * per));
 #define LAUNCH(TO, V)                                                                                           \
@@ -75,7 +99,7 @@ extern "C" int llm_short_conv(const float* x, const float* w, void* out, int out
 
 // One block a token.  The row alpha * x + y is held in shared memory between the pass that sums its squares and the
 // pass that scales it.
-template <typename TY>
+template <typename TY, bool VEC>
 __global__ void scaled_add_norm_kernel(
     float* __restrict__ x, const TY* __restrict__ y, long long y_stride, int parts, long long part_stride,
     const float* __restrict__ w, float alpha, float eps, float* __restrict__ kept, long long kept_slot_stride, int ring_rows,
@@ -95,18 +119,53 @@ __global__ void scaled_add_norm_kernel(
                    static_cast<size_t>(positions[t] % ring_rows) * width;
     }
     float ss = 0.0f;
-    for (int i = threadIdx.x; i < width; i += blockDim.x) {
-        const float old = xr[i];
-        float add = 0.0f;
-        for (int z = 0; z < parts; ++z) add += to_f32(yr[z * part_stride + i]);
-        const float v = alpha * old + add;
-        if (keep) keep[i] = old;
-        row[i] = v;
-        ss += v * v;
+    if (VEC) {                                              // four channels a thread, 16-byte loads; the same additions
+        for (int i = threadIdx.x * 4; i < width; i += blockDim.x * 4) {
+            const float4 old = *reinterpret_cast<const float4*>(xr + i);
+            float add[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll 4
+            for (int z = 0; z < parts; ++z) {
+                float v[4];
+                if constexpr (sizeof(TY) == 4) {
+                    const float4 f = *reinterpret_cast<const float4*>(yr + z * part_stride + i);
+                    v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
+                } else {
+                    const uint2 u = *reinterpret_cast<const uint2*>(yr + z * part_stride + i);
+                    v[0] = __uint_as_float(u.x << 16); v[1] = __uint_as_float(u.x & 0xffff0000u);
+                    v[2] = __uint_as_float(u.y << 16); v[3] = __uint_as_float(u.y & 0xffff0000u);
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) add[u] += v[u];
+            }
+            const float4 v = make_float4(alpha * old.x + add[0], alpha * old.y + add[1], alpha * old.z + add[2], alpha * old.w + add[3]);
+            if (keep) *reinterpret_cast<float4*>(keep + i) = old;
+            *reinterpret_cast<float4*>(row + i) = v;
+            ss += v.x * v.x;
+            ss += v.y * v.y;
+            ss += v.z * v.z;
+            ss += v.w * v.w;
+        }
+    } else {
+        for (int i = threadIdx.x; i < width; i += blockDim.x) {
+            const float old = xr[i];
+            float add = 0.0f;
+            for (int z = 0; z < parts; ++z) add += to_f32(yr[z * part_stride + i]);
+            const float v = alpha * old + add;
+            if (keep) keep[i] = old;
+            row[i] = v;
+            ss += v * v;
+        }
     }
     const float total = block_sum(ss, scratch);
     const float inv = 1.0f / sqrtf(total / static_cast<float>(width) + eps);
-    for (int i = threadIdx.x; i < width; i += blockDim.x) xr[i] = row[i] * inv * w[i];
+    if (VEC) {
+        for (int i = threadIdx.x * 4; i < width; i += blockDim.x * 4) {
+            const float4 v = *reinterpret_cast<const float4*>(row + i), ww = *reinterpret_cast<const float4*>(w + i);
+            *reinterpret_cast<float4*>(xr + i) = make_float4(v.x * inv * ww.x, v.y * inv * ww.y, v.z * inv * ww.z, v.w * inv * ww.w);
+        }
+    } else {
+        for (int i = threadIdx.x; i < width; i += blockDim.x) xr[i] = row[i] * inv * w[i];
+    }
 }
 
 extern "C" int llm_scaled_add_norm(float* x, const void* y, int y_dtype, long long y_stride, int parts,
@@ -120,9 +179,13 @@ extern "C" int llm_scaled_add_norm(float* x, const void* y, int y_dtype, long lo
     if (smem > 200 * 1024) return LLM_REFUSED_SIZE;
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     const int threads = width >= 2048 ? 512 : CN_THREADS;
+    const bool vec = width % 4 == 0 && aligned16(x) && aligned16(y) && aligned16(w) && y_stride % 4 == 0 && part_stride % 4 == 0 &&
+                     (!kept || (aligned16(kept) && kept_slot_stride % 4 == 0));
 #define LAUNCH(TY)                                                                                                 \
+    do { if (vec) LAUNCH_V(TY, true); else LAUNCH_V(TY, false); } while (0)
+#define LAUNCH_V(TY, VEC)                                                                                          \
     do {                                                                                                           \
-        auto kern = scaled_add_norm_kernel<TY>;                                                                    \
+        auto kern = scaled_add_norm_kernel<TY, VEC>;                                                                 \
         if (smem > 48 * 1024) {                                                                                    \
             const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,          \
                                                        static_cast<int>(smem));                                    \
@@ -136,5 +199,6 @@ extern "C" int llm_scaled_add_norm(float* x, const void* y, int y_dtype, long lo
     else if (y_dtype == LLM_DT_BF16) LAUNCH(bf16);
     else return LLM_REFUSED_DTYPE;
 #undef LAUNCH
+#undef LAUNCH_V
     return launch_status();
 }

@@ -397,25 +397,41 @@ __global__ void __launch_bounds__(2 * LM_GROUP_THREADS) latent_attention_mma_ker
 }
 
 // out[t, h, :] = sum_z 2^(m_z - M) acc_z / sum_z 2^(m_z - M) l_z over the splits of (t, h); M the largest m_z.
+// One warp a (token, head); the loops run over all LM_MAX_SPLITS with a predicate, so that the loads of the splits
+// are in flight together; what an empty split left in `part_acc` is never read.
 __global__ void latent_attention_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
-                                              bf16* __restrict__ out, int H, int R, int splits) {
+                                              bf16* __restrict__ out, int H, int R, int splits, int pairs) {
     pdl_begin();
-    const int t = blockIdx.x, h = blockIdx.y;
+    const int lane = threadIdx.x & 31, pair = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (pair >= pairs) return;
+    const int t = pair / H, h = pair - t * H;
     const size_t base = static_cast<size_t>(t) * splits * H + h;        // split z sits at base + z * H
-    float M = -CUDART_INF_F;
-    for (int z = 0; z < splits; ++z) M = fmaxf(M, part_ml[(base + static_cast<size_t>(z) * H) * 2]);
-    float wz[LM_MAX_SPLITS], L = 0.0f;
-    for (int z = 0; z < splits; ++z) {
-        const float m = part_ml[(base + static_cast<size_t>(z) * H) * 2];
-        wz[z] = (m == -CUDART_INF_F) ? 0.0f : exp2f(m - M);
-        L += wz[z] * part_ml[(base + static_cast<size_t>(z) * H) * 2 + 1];
+    float mz[LM_MAX_SPLITS], M = -CUDART_INF_F, L = 0.0f;
+#pragma unroll
+    for (int z = 0; z < LM_MAX_SPLITS; ++z) {
+        mz[z] = z < splits ? part_ml[(base + static_cast<size_t>(z) * H) * 2] : -CUDART_INF_F;
+        M = fmaxf(M, mz[z]);
+    }
+#pragma unroll
+    for (int z = 0; z < LM_MAX_SPLITS; ++z) {
+        const float l = z < splits ? part_ml[(base + static_cast<size_t>(z) * H) * 2 + 1] : 0.0f;
+        mz[z] = (mz[z] == -CUDART_INF_F) ? 0.0f : exp2f(mz[z] - M);     // from here on: the split's weight
+        L += mz[z] * l;
     }
     const float inv = 1.0f / L;
-    for (int col = threadIdx.x; col < R; col += blockDim.x) {
-        float a = 0.0f;
-        for (int z = 0; z < splits; ++z)
-            if (wz[z] != 0.0f) a += wz[z] * part_acc[(base + static_cast<size_t>(z) * H) * R + col];
-        out[(static_cast<size_t>(t) * H + h) * R + col] = __float2bfloat16(a * inv);
+    for (int col = lane * 2; col < R; col += 64) {
+        float2 v[LM_MAX_SPLITS];
+#pragma unroll
+        for (int z = 0; z < LM_MAX_SPLITS; ++z)
+            v[z] = mz[z] != 0.0f ? *reinterpret_cast<const float2*>(part_acc + (base + static_cast<size_t>(z) * H) * R + col)
+                                 : make_float2(0.0f, 0.0f);
+        float a0 = 0.0f, a1 = 0.0f;
+#pragma unroll
+        for (int z = 0; z < LM_MAX_SPLITS; ++z) {
+            a0 += mz[z] * v[z].x;
+            a1 += mz[z] * v[z].y;
+        }
+        *reinterpret_cast<__nv_bfloat162*>(out + (static_cast<size_t>(t) * H + h) * R + col) = __floats2bfloat162_rn(a0 * inv, a1 * inv);
     }
 }
 
@@ -473,7 +489,8 @@ extern "C" int llm_latent_attention(const void* q, void* out, float* part_acc, f
     if (R == 64) LAUNCH(1) else if (R == 128) LAUNCH(2) else if (R == 256) LAUNCH(4) else LAUNCH(8)
 #undef LAUNCH
     if (splits > 1)
-        launch_pdl(latent_attention_merge_kernel, dim3(num_tokens, H), dim3(R >= 128 ? 128 : 64), 0, s,
-                   static_cast<const float*>(part_acc), static_cast<const float*>(part_ml), static_cast<bf16*>(out), H, R, splits);
+        launch_pdl(latent_attention_merge_kernel, dim3((num_tokens * H + 3) / 4), dim3(128), 0, s,
+                   static_cast<const float*>(part_acc), static_cast<const float*>(part_ml), static_cast<bf16*>(out), H, R, splits,
+                   num_tokens * H);
     return launch_status();
 }
