@@ -673,6 +673,9 @@ def komazen_bench(args, pk, measure) -> int:
               d ** -0.5, status)
     add("prompt attention with temperature + logarithmic bias (new; mma.sync): 2048 tokens",
         lambda: ops.paged_attention_prefill_biased(qa, oa, 0, *common, dist_bias_t=three, analytic_bias=True), flops=attn_flops)
+    if ops.prefill_tcgen05_biased_supported(d, PAGE, heads // kv):
+        add("prompt attention with temperature + logarithmic bias (new; tcgen05, what the design's prompt portions take): 2048 tokens",
+            lambda: ops.paged_attention_prefill_tcgen05_biased(qa, oa, *common, three), flops=attn_flops)
     add("prompt attention, the same mma.sync kernel without them (like)", lambda: ops.paged_attention_prefill(qa, oa, *common),
         flops=attn_flops)
     if ops.prefill_tcgen05_supported(d, PAGE):

@@ -441,12 +441,20 @@ __device__ __forceinline__ void t5_st32(unsigned taddr, const unsigned (&r)[32])
         "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]) : "memory");
 }
 
+// BIAS: the scores carry more than the scale.  `head_bias` is float32 [nq][3] = (t, r1, r2) per query head and the
+// weight of key j for the query at position i is exp(S * scale * t - r1 * ln(1 + r2 * (i - j))).  The bias depends on
+// the head and on i - j only, and a tile of 128 rows by 128 keys meets 255 distances: the 256 softmax threads of a
+// head work out one each (a logarithm a thread a tile instead of 64) into a table in shared memory for the NEXT tile,
+// before the barrier that they all pass once a tile.  Three tables take turns: a thread that is late with tile j
+// may still read table j after that barrier (when it has to fetch its scores a second time) while an early one
+// already writes the table of tile j + 2.
+template <bool BIAS>
 __global__ void __launch_bounds__(T5O_THREADS, 1) paged_prefill_attention_tcgen05_online_kernel(
     const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap kv_map, bf16* __restrict__ out,
     const int32_t* __restrict__ tiles, const int32_t* __restrict__ entry_slot, const int32_t* __restrict__ entry_q_start,
     const int32_t* __restrict__ entry_q_len, const int32_t* __restrict__ entry_kv_len,
     const int32_t* __restrict__ block_table, int table_stride, int nq, int nkv, int page_size, int window,
-    float scale_log2e, int num_pages, int32_t* __restrict__ status) {
+    float scale_log2e, int num_pages, int32_t* __restrict__ status, const float* __restrict__ head_bias) {
     pdl_begin();
     constexpr int STAGES = T5O_STAGES;
     constexpr unsigned TMEM_COLS = 512;                           // S0 S1 O0 O1, 128 columns each
@@ -463,6 +471,7 @@ __global__ void __launch_bounds__(T5O_THREADS, 1) paged_prefill_attention_tcgen0
     __shared__ int abort_flag;
     __shared__ float x_max[2][2][2][128];                         // [tile parity][head][column half][row]: the halves' maxima
     __shared__ float x_sum[2][2][128];                            // [head][column half][row]: the halves' row sums, at the end
+    __shared__ float bias_tbl[BIAS ? 3 : 1][2][BIAS ? 256 : 1];   // [tile mod 3][head][i - j - (first row - first key of the tile) + 127]
 
     const int tile = blockIdx.y;
     const int h0 = blockIdx.x * 2;                                // first of this CTA's two query heads
@@ -644,8 +653,35 @@ __global__ void __launch_bounds__(T5O_THREADS, 1) paged_prefill_attention_tcgen0
         const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
         float m = -CUDART_INF_F, l = 0.0f;                        // m: the reference maximum, in units of log2
         bool ok = true;
+        // with BIAS the scores are turned into their final form (units of log2) as they arrive, and `eff` is 1
+        float sc = scale_log2e, r1 = 0.0f, r2 = 0.0f;
+        if constexpr (BIAS) {
+            const float* hb = head_bias + static_cast<size_t>(h0 + g) * 3;
+            sc *= hb[0]; r1 = hb[1]; r2 = hb[2];
+        }
+        const float eff = BIAS ? 1.0f : scale_log2e;
+        const int in_head = (wl & 7) * 32 + lane;                 // 0..255 among the head's softmax threads
+        auto fill_table = [&](int jt, int which) {                // the distances of tile jt: first row - first key - 127 + in_head
+            const int dist = pos_first - (k_lo + jt * T5O_BN) - 127 + in_head;
+            bias_tbl[which][g][in_head] = dist > 0 ? r1 * __log2f(fmaf(r2, static_cast<float>(dist), 1.0f)) : 0.0f;
+        };
+        int tb_cur = 0;
+        if constexpr (BIAS) {
+            fill_table(0, 0);
+            asm volatile("bar.sync %0, 256;\n" ::"r"(1 + g) : "memory");
+        }
         for (int j = 0; j < n_tiles; ++j) {
             const int kt = k_lo + j * T5O_BN + half * 64;         // this thread's first key of the tile
+            const int tb_next = tb_cur == 2 ? 0 : tb_cur + 1;
+            if constexpr (BIAS) {
+                if (j + 1 < n_tiles) fill_table(j + 1, tb_next);
+            }
+            // S of (row, column c + i of this thread's 64) -> S * scale * t - bias(i - j), in place
+            auto biased = [&](unsigned (&r)[32], int c) {
+                const float* tb = &bias_tbl[tb_cur][g][row - (half * 64 + c) + 127];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(fmaf(__uint_as_float(r[i]), sc, -tb[-i]));
+            };
             // After a wait has run out (ok false) a thread still passes every barrier below, the same
             // number of times as the others, and touches nothing else.
             if (ok && !t5_wait(&s_full[g], j & 1, &abort_flag, status, row_base)) ok = false;
@@ -657,6 +693,7 @@ __global__ void __launch_bounds__(T5O_THREADS, 1) paged_prefill_attention_tcgen0
                 t5_ld32(my_s, ra);
                 t5_ld32(my_s + 32, rb);
                 t5_wait_ld();
+                if constexpr (BIAS) { biased(ra, 0); biased(rb, 32); }
                 if (full_tile) {
 #pragma unroll
                     for (int i = 0; i < 32; ++i) mx = fmaxf(mx, fmaxf(__uint_as_float(ra[i]), __uint_as_float(rb[i])));
@@ -670,8 +707,10 @@ __global__ void __launch_bounds__(T5O_THREADS, 1) paged_prefill_attention_tcgen0
                 x_max[j & 1][g][half][row] = mx;
             }
             asm volatile("bar.sync %0, 256;\n" ::"r"(1 + g) : "memory");      // the 8 softmax warps of this head
+            const int tb_mine = tb_cur;
+            tb_cur = tb_next;
             if (!ok) continue;
-            mx = fmaxf(mx, x_max[j & 1][g][half ^ 1][row]) * scale_log2e;     // scale > 0; -inf stays -inf
+            mx = fmaxf(mx, x_max[j & 1][g][half ^ 1][row]) * eff;             // scale > 0; -inf stays -inf
             // move the reference up only when the maximum has run away from it (both threads of a row
             // see the same numbers and decide alike)
             const bool adopt = (m == -CUDART_INF_F) && (mx > m);  // nothing accumulated under the old reference
@@ -693,6 +732,11 @@ __global__ void __launch_bounds__(T5O_THREADS, 1) paged_prefill_attention_tcgen0
                 t5_wait_st();
                 t5_ld32(my_s, ra);
                 t5_wait_ld();
+                if constexpr (BIAS) {
+                    const float* tb = &bias_tbl[tb_mine][g][row - half * 64 + 127];
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) ra[i] = __float_as_uint(fmaf(__uint_as_float(ra[i]), sc, -tb[-i]));
+                }
             }
             if (adopt || jump) m = mx;
             const float msub = (m == -CUDART_INF_F) ? 0.0f : m;
@@ -702,8 +746,8 @@ __global__ void __launch_bounds__(T5O_THREADS, 1) paged_prefill_attention_tcgen0
                 if (full_tile) {
 #pragma unroll
                     for (int i = 0; i < 32; i += 2) {
-                        const float x0 = fmaf(__uint_as_float(r[i]), scale_log2e, -msub);
-                        const float x1 = fmaf(__uint_as_float(r[i + 1]), scale_log2e, -msub);
+                        const float x0 = fmaf(__uint_as_float(r[i]), eff, -msub);
+                        const float x1 = fmaf(__uint_as_float(r[i + 1]), eff, -msub);
                         const float p0 = t5_ex2(x0), p1 = t5_ex2(x1);     // (a cubic on the FMA pipe for a share of them: measured slower)
                         l += p0 + p1;
                         pk[i >> 1] = t5_pack(p0, p1);
@@ -712,8 +756,8 @@ __global__ void __launch_bounds__(T5O_THREADS, 1) paged_prefill_attention_tcgen0
 #pragma unroll
                     for (int i = 0; i < 32; i += 2) {
                         const int key = kt + c + i;
-                        const float p0 = (key <= pos && key >= lo) ? t5_ex2(fmaf(__uint_as_float(r[i]), scale_log2e, -msub)) : 0.0f;
-                        const float p1 = (key + 1 <= pos && key + 1 >= lo) ? t5_ex2(fmaf(__uint_as_float(r[i + 1]), scale_log2e, -msub)) : 0.0f;
+                        const float p0 = (key <= pos && key >= lo) ? t5_ex2(fmaf(__uint_as_float(r[i]), eff, -msub)) : 0.0f;
+                        const float p1 = (key + 1 <= pos && key + 1 >= lo) ? t5_ex2(fmaf(__uint_as_float(r[i + 1]), eff, -msub)) : 0.0f;
                         l += p0 + p1;
                         pk[i >> 1] = t5_pack(p0, p1);
                     }
@@ -796,13 +840,20 @@ extern "C" int llm_paged_prefill_tcgen05_supported(int d, int page_size) {
 }
 extern "C" int llm_paged_prefill_tcgen05_tile_rows() { return T5_BM; }
 
+// The scores' additions (a temperature per head, a logarithmic distance bias) are built into the kernel that serves
+// two heads of a group at once.
+extern "C" int llm_paged_prefill_tcgen05_biased_supported(int d, int page_size, int group) {
+    return llm_paged_prefill_tcgen05_supported(d, page_size) && group > 0 && group % 2 == 0;
+}
+
 // q, out: bfloat16 [num_tokens, nq*128]; cache: bfloat16 [pages, 2, nkv, page_size, 128];
 // tiles: int32 [n_tiles][2] = (entry, first query row of the tile inside the entry), 128 rows each.
-extern "C" int llm_paged_attention_prefill_tcgen05(
+// head_bias: null, or float32 [nq][3] = (temperature, r1, r2) per query head (even groups only).
+static int t5_launch(
     const void* q, void* out, const void* cache, int num_tokens, const int32_t* tiles, int n_tiles,
     const int32_t* entry_slot, const int32_t* entry_q_start, const int32_t* entry_q_len, const int32_t* entry_kv_len,
     const int32_t* block_table, int table_stride, int nq, int nkv, int d, int page_size, int window, float scale,
-    int num_pages, int32_t* status, uintptr_t stream) {
+    int num_pages, int32_t* status, const float* head_bias, uintptr_t stream) {
     if (n_tiles <= 0) return LLM_OK;
     if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || !llm_paged_prefill_tcgen05_supported(d, page_size) || nq > 65535 ||
         n_tiles > 65535)
@@ -815,6 +866,7 @@ extern "C" int llm_paged_attention_prefill_tcgen05(
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     const float sl2 = scale * 1.4426950408889634f;
     const int group = nq / nkv;
+    if (head_bias && group % 2 != 0) return LLM_REFUSED_SIZE;
 #define T5_GO(HEADS, STAGES)                                                                                         \
     {                                                                                                                \
         const size_t smem = static_cast<size_t>(HEADS * 2 * T5_QHALF + 2 * STAGES * T5_TILE) * sizeof(bf16) + 1024;  \
@@ -828,15 +880,35 @@ extern "C" int llm_paged_attention_prefill_tcgen05(
     }
     if (group % 2 == 0) {                                           // two heads of a group share a CTA: the one-pass kernel
         const size_t smem = static_cast<size_t>(2 * 2 * T5_QHALF + 2 * T5O_STAGES * T5O_TILE) * sizeof(bf16) + 1024;
-        auto kern = paged_prefill_attention_tcgen05_online_kernel;
+        auto kern = head_bias ? paged_prefill_attention_tcgen05_online_kernel<true>
+                              : paged_prefill_attention_tcgen05_online_kernel<false>;
         const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
         if (e != cudaSuccess) return static_cast<int>(e);
         launch_pdl(kern, dim3(nq / 2, n_tiles), dim3(T5O_THREADS), smem, s, q_map, kv_map, static_cast<bf16*>(out), tiles,
                    entry_slot, entry_q_start, entry_q_len, entry_kv_len, block_table, table_stride, nq, nkv, page_size,
-                   window, sl2, num_pages, status);
+                   window, sl2, num_pages, status, head_bias);
         return launch_status();
     }
     T5_GO(1, 4)                                                     // odd groups: the two-pass kernel, one head per CTA
 #undef T5_GO
     return launch_status();
+}
+
+extern "C" int llm_paged_attention_prefill_tcgen05(
+    const void* q, void* out, const void* cache, int num_tokens, const int32_t* tiles, int n_tiles,
+    const int32_t* entry_slot, const int32_t* entry_q_start, const int32_t* entry_q_len, const int32_t* entry_kv_len,
+    const int32_t* block_table, int table_stride, int nq, int nkv, int d, int page_size, int window, float scale,
+    int num_pages, int32_t* status, uintptr_t stream) {
+    return t5_launch(q, out, cache, num_tokens, tiles, n_tiles, entry_slot, entry_q_start, entry_q_len, entry_kv_len,
+                     block_table, table_stride, nq, nkv, d, page_size, window, scale, num_pages, status, nullptr, stream);
+}
+
+extern "C" int llm_paged_attention_prefill_tcgen05_biased(
+    const void* q, void* out, const void* cache, int num_tokens, const int32_t* tiles, int n_tiles,
+    const int32_t* entry_slot, const int32_t* entry_q_start, const int32_t* entry_q_len, const int32_t* entry_kv_len,
+    const int32_t* block_table, int table_stride, int nq, int nkv, int d, int page_size, int window, float scale,
+    int num_pages, int32_t* status, const float* head_bias, uintptr_t stream) {
+    if (!head_bias) return LLM_REFUSED_SIZE;
+    return t5_launch(q, out, cache, num_tokens, tiles, n_tiles, entry_slot, entry_q_start, entry_q_len, entry_kv_len,
+                     block_table, table_stride, nq, nkv, d, page_size, window, scale, num_pages, status, head_bias, stream);
 }

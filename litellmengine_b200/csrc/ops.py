@@ -1188,6 +1188,38 @@ def paged_attention_prefill_tcgen05(q: torch.Tensor, out: torch.Tensor, cache: t
     return out
 
 
+def prefill_tcgen05_biased_supported(d: int, page_size: int, group: int) -> bool:
+    f = _fn("attention_prefill_tcgen05", "llm_paged_prefill_tcgen05_biased_supported", [c_int, c_int, c_int])
+    return bool(f(d, page_size, group))
+
+
+def paged_attention_prefill_tcgen05_biased(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, tiles: torch.Tensor,
+                                           n_tiles: int, entry_slot, entry_q_start, entry_q_len, entry_kv_len,
+                                           block_table: torch.Tensor, nq: int, nkv: int, d: int, page_size: int,
+                                           window: Optional[int], scale: float, status: torch.Tensor,
+                                           head_bias: torch.Tensor) -> torch.Tensor:
+    """`paged_attention_prefill_tcgen05` for scores with a temperature per head and a logarithmic distance bias:
+    `head_bias` float32 [nq, 3] = (t, r1, r2) per query head, weight of key j for the query at i =
+    exp(q.k * scale * t - r1 * ln(1 + r2 * (i - j))).  Even groups of query heads per kv head only; `out` is
+    bfloat16 [T, nq*d], contiguous."""
+    _dev(q, out, cache, tiles, entry_slot, entry_q_start, entry_q_len, entry_kv_len, block_table, status, head_bias)
+    if q.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+        raise KernelError("the tcgen05 prefill attention kernel is bfloat16 only")
+    if q.shape[1] != nq * d or tuple(cache.shape[1:]) != (2, nkv, page_size, d) or not out.is_contiguous() \
+            or tuple(out.shape) != tuple(q.shape):
+        raise KernelError("q and out must be [T, heads*head_dim] and cache [pages, 2, kv_heads, page_size, head_dim]")
+    if head_bias.dtype != torch.float32 or tuple(head_bias.shape) != (nq, 3) or not head_bias.is_contiguous():
+        raise KernelError("head_bias must be float32 [heads, 3]: temperature, r1, r2")
+    f = _fn("attention_prefill_tcgen05", "llm_paged_attention_prefill_tcgen05_biased",
+            [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+             c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_void_p])
+    _check(f(_ptr(q), _ptr(out), _ptr(cache), q.shape[0], _ptr(tiles), n_tiles, _ptr(entry_slot), _ptr(entry_q_start),
+             _ptr(entry_q_len), _ptr(entry_kv_len), _ptr(block_table), block_table.shape[1], nq, nkv, d, page_size,
+             int(window) if window else 0, float(scale), cache.shape[0], _ptr(status), _ptr(head_bias), _stream()),
+           "paged_attention_prefill_tcgen05_biased")
+    return out
+
+
 def argmax_rows(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     _dev(logits, out)
     if logits.dtype != torch.float32 or logits.dim() != 2:

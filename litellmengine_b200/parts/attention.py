@@ -397,7 +397,15 @@ class GatedAttentionMixer(BranchMixer):
             n_tiles = work.padded_tiles.shape[0] if padded else work.num_prefill_tiles
             n_dec = work.padded_rows.shape[0] if padded else work.num_decode
             gate = proj if s.output_gate else None
-            if n_tiles:
+            if (n_tiles and self.analytic and gate is None and out_col0 == 0 and out_scale == 1.0 and out.is_contiguous()
+                    and out.shape[1] == self.nq * self.d
+                    and ops.prefill_tcgen05_biased_supported(self.d, ctx.page_size, self.nq // self.nkv)):
+                # temperature and logarithmic bias in the softmax warps of the tcgen05 kernel (two heads of a group a CTA)
+                ops.paged_attention_prefill_tcgen05_biased(
+                    q, out, ctx.cache, work.padded_tiles if padded else work.prefill_tiles, n_tiles, b.entry_slot,
+                    b.entry_q_start, b.entry_q_len, b.entry_kv_len, ctx.block_table, self.nq, self.nkv, self.d,
+                    ctx.page_size, s.window, self.scale, ctx.status, self.dist_table_t)
+            elif n_tiles:
                 ops.paged_attention_prefill_biased(
                     q, out, out_col0, ctx.cache, work.padded_tiles if padded else work.prefill_tiles, n_tiles, b.entry_slot,
                     b.entry_q_start, b.entry_q_len, b.entry_kv_len, ctx.block_table, self.nq, self.nkv, self.d, ctx.page_size,

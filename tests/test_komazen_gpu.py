@@ -312,7 +312,7 @@ def test_attention_with_head_temperature_and_logarithmic_distance_bias():
     assert (flat[650] - pk.biased_attention_core(q, k, v, scale, temp, r1, r2)[650]).abs().max() > 0.1
 
 
-@pytest.mark.parametrize("d,group", [(64, 2), (128, 1), (128, 4)])
+@pytest.mark.parametrize("d,group", [(64, 2), (128, 1), (128, 2), (128, 4)])
 def test_tensor_core_attention_with_temperature_and_logarithmic_bias(d, group):
     """The kernels that a bfloat16 run takes at head sizes 64 and 128: a prompt portion that starts in the middle of a
     page with keys before it, and single tokens in the split-key decode kernel; the temperature and the bias are
@@ -346,6 +346,14 @@ def test_tensor_core_attention_with_temperature_and_logarithmic_bias(d, group):
                                        block_table, H, G, d, page, None, scale, status, dist_bias_t=three, analytic_bias=True)
     assert status.tolist() == [0, 0]
     assert (out.double().cpu().view(T, H, d) - ref).abs().max() < 0.06
+    if ops.prefill_tcgen05_biased_supported(d, page, group):
+        # the kernel with accumulators in tensor memory: the bias comes from a table by distance that the softmax
+        # threads renew tile by tile (here up to four tiles of 128 keys a row tile, so every table is used again)
+        o5 = torch.zeros(T, H * d, dtype=torch.bfloat16, device=DEV)
+        ops.paged_attention_prefill_tcgen05_biased(qd, o5, cache, tiles, tiles.shape[0], _i32([1]), _i32([0]), _i32([T]),
+                                                   _i32([N]), block_table, H, G, d, page, None, scale, status, three)
+        assert status.tolist() == [0, 0]
+        assert (o5.double().cpu().view(T, H, d) - ref).abs().max() < 0.06
     if ops.fast_attention_supported(d, group):
         for splits in (1, 3):
             a = torch.zeros(T, H * d, dtype=torch.bfloat16, device=DEV)
