@@ -32,48 +32,79 @@ __device__ __forceinline__ void load_row(float (&v)[V], const float* p) {       
     }
 }
 
-template <typename TO, int V>
+// TT consecutive tokens a block (a step of many tokens: their index lookups and row loads are in flight together,
+// which is what the kernel waits for; a short step takes TT = 1 and one block a token).  A row that does not exist
+// (before the sequence's start) is not added; its load is pointed at the token's own row.
+template <typename TO, int V, int TT>
 __global__ void short_conv_kernel(
     const float* __restrict__ x, const float* __restrict__ w, TO* __restrict__ out, const float* __restrict__ kept,
     long long kept_slot_stride, const int32_t* __restrict__ positions, const int32_t* __restrict__ token_entry,
-    const int32_t* __restrict__ entry_slot, const int32_t* __restrict__ entry_q_start, int width, int taps) {
+    const int32_t* __restrict__ entry_slot, const int32_t* __restrict__ entry_q_start, int num_tokens, int width, int taps) {
     pdl_begin();
-    const int t = blockIdx.x;
+    const int t0 = blockIdx.x * TT;
     const int c = (blockIdx.y * CN_THREADS + threadIdx.x) * V;
     if (c >= width) return;
-    const int e = token_entry[t];
-    const int q0 = entry_q_start[e], pos = positions[t];
     const int R = taps - 1;
-    const float* ring = kept ? kept + static_cast<size_t>(entry_slot[e]) * kept_slot_stride : nullptr;
-    float acc[V], cur[V];
-    load_row<V>(cur, x + static_cast<size_t>(t) * width + c);
+    int tok[TT], q0[TT], pos[TT];
+    const float* ring[TT];
 #pragma unroll
-    for (int u = 0; u < V; ++u) acc[u] = cur[u];
-    for (int back = R; back >= 1; --back) {                 // oldest first: the order of additions is fixed
-        const int j = taps - 1 - back;
-        const float* src;
-        if (t - back >= q0) src = x + static_cast<size_t>(t - back) * width + c;
-        else if (pos - back >= 0 && ring) src = ring + static_cast<size_t>((pos - back) % R) * width + c;
-        else continue;                                      // before the sequence's start: zero
-        float old[V];
-        load_row<V>(old, src);
-#pragma unroll
-        for (int u = 0; u < V; ++u) acc[u] += w[static_cast<size_t>(c + u) * taps + j] * old[u];
+    for (int i = 0; i < TT; ++i) {
+        tok[i] = min(t0 + i, num_tokens - 1);               // a block's spare tokens repeat the last one and store nothing
+        const int e = token_entry[tok[i]];
+        q0[i] = entry_q_start[e];
+        pos[i] = positions[tok[i]];
+        ring[i] = kept ? kept + static_cast<size_t>(entry_slot[e]) * kept_slot_stride : nullptr;
     }
+    float acc[TT][V], cur[TT][V];
 #pragma unroll
-    for (int u = 0; u < V; ++u) acc[u] += w[static_cast<size_t>(c + u) * taps + taps - 1] * cur[u];
-    TO* o = out + static_cast<size_t>(t) * width + c;
-    if constexpr (V == 4 && sizeof(TO) == 4) {
-        *reinterpret_cast<float4*>(o) = make_float4(acc[0], acc[1], acc[2], acc[3]);
-    } else if constexpr (V == 4 && sizeof(TO) == 2) {
-        __nv_bfloat162 lo2 = __floats2bfloat162_rn(acc[0], acc[1]), hi2 = __floats2bfloat162_rn(acc[2], acc[3]);
-        uint2 pk;
-        pk.x = *reinterpret_cast<unsigned*>(&lo2);
-        pk.y = *reinterpret_cast<unsigned*>(&hi2);
-        *reinterpret_cast<uint2*>(o) = pk;
-    } else {
+    for (int i = 0; i < TT; ++i) {
+        load_row<V>(cur[i], x + static_cast<size_t>(tok[i]) * width + c);
 #pragma unroll
-        for (int u = 0; u < V; ++u) o[u] = from_f32<TO>(acc[u]);
+        for (int u = 0; u < V; ++u) acc[i][u] = cur[i][u];
+    }
+    for (int back = R; back >= 1; --back) {                 // oldest first: the order of additions is fixed
+        float wj[V], old[TT][V];
+        bool there[TT];
+#pragma unroll
+        for (int u = 0; u < V; ++u) wj[u] = w[static_cast<size_t>(c + u) * taps + taps - 1 - back];
+#pragma unroll
+        for (int i = 0; i < TT; ++i) {
+            const float* src = x + static_cast<size_t>(tok[i]) * width + c;
+            there[i] = true;
+            if (tok[i] - back >= q0[i]) src = x + static_cast<size_t>(tok[i] - back) * width + c;
+            else if (pos[i] - back >= 0 && ring[i]) src = ring[i] + static_cast<size_t>((pos[i] - back) % R) * width + c;
+            else there[i] = false;                          // before the sequence's start: zero
+            load_row<V>(old[i], src);
+        }
+#pragma unroll
+        for (int i = 0; i < TT; ++i) {
+            if (there[i]) {
+#pragma unroll
+                for (int u = 0; u < V; ++u) acc[i][u] += wj[u] * old[i][u];
+            }
+        }
+    }
+    float wl[V];
+#pragma unroll
+    for (int u = 0; u < V; ++u) wl[u] = w[static_cast<size_t>(c + u) * taps + taps - 1];
+#pragma unroll
+    for (int i = 0; i < TT; ++i) {
+        if (t0 + i >= num_tokens) break;
+#pragma unroll
+        for (int u = 0; u < V; ++u) acc[i][u] += wl[u] * cur[i][u];
+        TO* o = out + static_cast<size_t>(t0 + i) * width + c;
+        if constexpr (V == 4 && sizeof(TO) == 4) {
+            *reinterpret_cast<float4*>(o) = make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
+        } else if constexpr (V == 4 && sizeof(TO) == 2) {
+            __nv_bfloat162 lo2 = __floats2bfloat162_rn(acc[i][0], acc[i][1]), hi2 = __floats2bfloat162_rn(acc[i][2], acc[i][3]);
+            uint2 pk;
+            pk.x = *reinterpret_cast<unsigned*>(&lo2);
+            pk.y = *reinterpret_cast<unsigned*>(&hi2);
+            *reinterpret_cast<uint2*>(o) = pk;
+        } else {
+#pragma unroll
+            for (int u = 0; u < V; ++u) o[u] = from_f32<TO>(acc[i][u]);
+        }
     }
 }
 
@@ -86,12 +117,13 @@ extern "C" int llm_short_conv(const float* x, const float* w, void* out, int out
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     const bool four = width % 4 == 0 && aligned16(x) && aligned16(out) && (!kept || (aligned16(kept) && kept_slot_stride % 4 == 0));
     const int per = four ? 4 : 1;
-    const dim3 grid(num_tokens, (width + CN_THREADS * per - 1) / (CN_THREADS * per));
-#define LAUNCH(TO, V)                                                                                           \
-    launch_pdl((short_conv_kernel<TO, V>), grid, dim3(CN_THREADS), 0, s, x, w, static_cast<TO*>(out), kept,      \
-               kept_slot_stride, positions, token_entry, entry_slot, entry_q_start, width, taps)
-    if (out_dtype == LLM_DT_F32) { if (four) LAUNCH(float, 4); else LAUNCH(float, 1); }
-    else if (out_dtype == LLM_DT_BF16) { if (four) LAUNCH(bf16, 4); else LAUNCH(bf16, 1); }
+    const bool many = four && num_tokens >= 256;            // four tokens a block
+    const dim3 grid(many ? (num_tokens + 3) / 4 : num_tokens, (width + CN_THREADS * per - 1) / (CN_THREADS * per));
+#define LAUNCH(TO, V, TT)                                                                                       \
+    launch_pdl((short_conv_kernel<TO, V, TT>), grid, dim3(CN_THREADS), 0, s, x, w, static_cast<TO*>(out), kept,  \
+               kept_slot_stride, positions, token_entry, entry_slot, entry_q_start, num_tokens, width, taps)
+    if (out_dtype == LLM_DT_F32) { if (many) LAUNCH(float, 4, 4); else if (four) LAUNCH(float, 4, 1); else LAUNCH(float, 1, 1); }
+    else if (out_dtype == LLM_DT_BF16) { if (many) LAUNCH(bf16, 4, 4); else if (four) LAUNCH(bf16, 4, 1); else LAUNCH(bf16, 1, 1); }
     else return LLM_REFUSED_DTYPE;
 #undef LAUNCH
     return launch_status();

@@ -32,26 +32,30 @@ __global__ void latent_prepare_kernel(
     __shared__ float scratch[33];
     const int t = blockIdx.x;
     const float* row = proj + static_cast<size_t>(t) * proj_stride;
+    // the page lookup and both latents' loads are started before anything waits: the kernel is bound by their latency
+    int pos = 0, page = -1;
+    if (keys) {
+        pos = positions[t];
+        const int slot = entry_slot[token_entry[t]];
+        const int logical = pos / page_size;
+        page = logical < table_stride ? block_table[static_cast<size_t>(slot) * table_stride + logical] : -1;
+    }
+    float ss = 0.0f, ss_kv = 0.0f;
+    for (int i = threadIdx.x; i < Q; i += blockDim.x) { const float a = row[dq_off + i]; ss += a * a; }
+    if (keys)
+        for (int i = threadIdx.x; i < R; i += blockDim.x) { const float a = row[dkv_off + i]; ss_kv += a * a; }
     {
-        float ss = 0.0f;
-        for (int i = threadIdx.x; i < Q; i += blockDim.x) { const float a = row[dq_off + i]; ss += a * a; }
         const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / static_cast<float>(Q) + eps);
         for (int i = threadIdx.x; i < Q; i += blockDim.x)
             cq_out[static_cast<size_t>(t) * Q + i] = from_f32<TQ>(row[dq_off + i] * inv * wq[i]);
     }
     if (!keys) return;
-    const int pos = positions[t];
-    const int slot = entry_slot[token_entry[t]];
-    const int logical = pos / page_size;
-    const int page = logical < table_stride ? block_table[static_cast<size_t>(slot) * table_stride + logical] : -1;
     if (page < 0 || page >= num_pages) {
         if (threadIdx.x == 0 && atomicCAS(status, 0, 3) == 0) status[1] = t;
         return;
     }
     TC* dst = keys + static_cast<size_t>(page) * key_page_stride + static_cast<size_t>(pos % page_size) * (R + P);
-    float ss = 0.0f;
-    for (int i = threadIdx.x; i < R; i += blockDim.x) { const float a = row[dkv_off + i]; ss += a * a; }
-    const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / static_cast<float>(R) + eps);
+    const float inv = 1.0f / sqrtf(block_sum(ss_kv, scratch) / static_cast<float>(R) + eps);
     for (int i = threadIdx.x; i < R; i += blockDim.x) dst[i] = from_f32<TC>(row[dkv_off + i] * inv * wkv[i]);
     const float* kr = row + dkv_off + R;
     const int half = dims / 2;

@@ -83,6 +83,15 @@ KOMA_E = _config(97, 72, 1e-5, 2.0, 1.5, 3, [
 ])
 KOMA_E_PAGE = 32
 
+# F: attention heads of 128, which the bfloat16 run takes on the tensor cores: two query heads a key head (prompt portions
+# on the kernel with accumulators in tensor memory) and one (the mma.sync kernel); a latent of 256
+KOMA_F = _config(113, 64, 1e-5, 4.0, 2.0, 3, [
+    _layer("attention", _attn(4, 2, 128, 128, 0.09), 96),
+    _layer("latent_attention", _latent(4, 16, 32, 24, 40, 256, 0.2, 140, 5000.0), 80),
+    _layer("attention", _attn(2, 2, 128, 128, 0.08), None),
+])
+KOMA_F_PAGE = 16
+
 
 def tensor_shapes(cfg: dict) -> Dict[str, tuple]:
     """Names and shapes of a model's tensors, written out from the design's naming rules."""

@@ -17,7 +17,7 @@ DEV = "cuda:0"
 F64 = torch.float64
 
 CASES = {"A": (km.KOMA_A, km.KOMA_A_PAGE, 3), "B": (km.KOMA_B, km.KOMA_B_PAGE, 5), "C": (km.KOMA_C, km.KOMA_C_PAGE, 9),
-         "D": (km.KOMA_D, km.KOMA_D_PAGE, 11), "E": (km.KOMA_E, km.KOMA_E_PAGE, 13)}
+         "D": (km.KOMA_D, km.KOMA_D_PAGE, 11), "E": (km.KOMA_E, km.KOMA_E_PAGE, 13), "F": (km.KOMA_F, km.KOMA_F_PAGE, 17)}
 # root mean square over the vocabulary of (difference minus its mean), as a fraction of the reference logits'
 # spread; the float32 run is measured against the plain code in double precision
 LIMIT = {"float32": 1e-4, "bfloat16": 0.12}
@@ -78,7 +78,7 @@ def requests(cfg, lengths, seed):
 
 # ---- whole models, every cutting ------------------------------------------------------------------
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("case", ["A", "B", "C", "D", "E"])
+@pytest.mark.parametrize("case", ["A", "B", "C", "D", "E", "F"])
 def test_every_cutting_matches_plain(case, dtype):
     cfg, page, w = model_of(case)
     reqs = requests(cfg, [1, 2, 3, 37, 90, 150], seed=1)
@@ -102,6 +102,18 @@ def test_long_prompt_and_window_over_pages(dtype):
                         ("portions", rh.trace_portions(reqs, seed=5, sizes=(2, 61, 64, 65, 128, 257, 300)))):
         runner = rh.make_runner(cfg, w, dtype, page, rh.peak_tokens(steps, round_to=page), max_requests=2)
         assert_close(rh.run_trace(runner, steps), ref, dtype, name)
+
+
+def test_long_prompt_through_the_tensor_core_attention_kernels():
+    """450 tokens with attention heads of 128 in bfloat16: row tiles of 128 that walk up to four tiles of 128 keys with the
+    bias table renewed for each, portions that start in the middle of a page and of a tile, decoded tokens after them."""
+    cfg, page, w = model_of("F")
+    reqs = requests(cfg, [450, 260], seed=8)
+    ref = Reference(cfg, w, reqs, "bfloat16")
+    for name, steps in (("whole", rh.trace_whole(reqs)), ("decode", rh.trace_tail_decode(reqs, tail=40)),
+                        ("portions", rh.trace_portions(reqs, seed=9, sizes=(2, 61, 127, 128, 129, 257)))):
+        runner = rh.make_runner(cfg, w, "bfloat16", page, rh.peak_tokens(steps, round_to=page), max_requests=2)
+        assert_close(rh.run_trace(runner, steps), ref, "bfloat16", name)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
