@@ -415,13 +415,17 @@ class GatedAttentionMixer(BranchMixer):
                 return
             rows = work.padded_rows if padded else (None if n_dec == b.num_tokens else work.decode_rows)
             if self._tuned_decode and not n_tiles:
-                a = torch.empty_like(q)
+                # without a gate, a scale or a column offset the kernel writes where the output product reads
+                direct = (gate is None and out_col0 == 0 and out_scale == 1.0 and out.is_contiguous()
+                          and tuple(out.shape) == tuple(q.shape))
+                a = out if direct else torch.empty_like(q)
                 splits = decode_key_splits(q.device, n_dec, self.nkv, self._decode_reach(b))
                 ops.paged_attention_decode(q, a, ctx.cache, rows, n_dec, b.positions, b.token_entry, b.entry_slot,
                                            ctx.block_table, self.nq, self.nkv, self.d, ctx.page_size, s.window, self.scale, splits,
                                            ctx.status, dist_bias_t=self.dist_table_t, analytic_bias=self.analytic)
-                ops.gate_mul(a, gate, col0 + self.g_off, out, out_col0, s.output_gate, out_scale,
-                             per_head=self.dv if self.gate_per_head else 0)
+                if not direct:
+                    ops.gate_mul(a, gate, col0 + self.g_off, out, out_col0, s.output_gate, out_scale,
+                                 per_head=self.dv if self.gate_per_head else 0)
                 return
         else:
             rows = None
