@@ -98,6 +98,7 @@ class PagedNeed:
     head_dim: int
     window: Optional[int] = None      # None: every earlier position stays; w: only the last w
     value_dim: Optional[int] = None
+    keep_first: int = 0               # with a window: the first so many positions of a request stay all the same
 
     @property
     def key_width(self) -> int:
@@ -149,7 +150,10 @@ class CacheGroup:
         return (length + self.page_size - 1) // self.page_size
 
     def held_pages(self, slot: int) -> List[int]:
-        return [int(p) for p in self.table[slot, self.first_held[slot]:self.num_logical[slot]]]
+        lo, hi = int(self.first_held[slot]), int(self.num_logical[slot])
+        head = self.pages_for(self.need.keep_first) if self.need.window is not None else 0
+        kept = list(range(head)) if lo > head else []          # the head's pages stay when the window moves on
+        return [int(self.table[slot, i]) for i in kept + list(range(lo, hi))]
 
 
 def _needs_of(need) -> list:
@@ -224,6 +228,8 @@ class CacheManager:
         if not self._h:
             raise CacheError(host.last_error())
         for i, g in enumerate(self.groups):
+            if g.need.window is not None and g.need.keep_first:
+                _check(self._lib.hc_cache_set_head(self._h, i, int(g.need.keep_first)))
             g._bind(self._lib, self._h, i, max_slots, max_pages_per_request)
         self.state: Dict[object, object] = {}     # stage index or name -> device tensor [max_slots, *shape]
         self._extra_state = dict(extra_state or {})

@@ -8,10 +8,11 @@ from .qwen3 import Qwen3Config
 from .tobovik import TobovikConfig
 from .gubidra import GubidraConfig
 from .komazen import KomazenConfig
+from .vugedra import VugedraConfig
 
 __all__ = [
     "ConfigError", "config_class_for", "config_from_dict", "load_config",
     "register_architecture", "registered_architectures", "save_config",
     "unregister_architecture", "BlockSpec", "FeedForwardSpec", "MixerSpec", "ModelPlan",
-    "NormSpec", "PositionSpec", "StageSpec", "Qwen3Config", "TobovikConfig", "GubidraConfig", "KomazenConfig",
+    "NormSpec", "PositionSpec", "StageSpec", "Qwen3Config", "TobovikConfig", "GubidraConfig", "KomazenConfig", "VugedraConfig",
 ]

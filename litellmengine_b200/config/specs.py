@@ -25,6 +25,7 @@ class NormSpec:
     eps: float
     weight_name: str = "weight"
     # kind 'layernorm': (x - mean) * rsqrt(mean((x - mean)^2) + eps) * w, a weight and no bias.
+    # kind 'tanh': tanh(alpha * x) * w + b elementwise, no mean and no variance; tensors '<weight>', 'alpha' [], 'b'.
 
 
 @dataclass(frozen=True)
@@ -35,6 +36,11 @@ class PositionSpec:
     position * theta**(-2i/rotary_dim).  kind 'none': no encoding.  kind 'sinusoid_added' (a model's
     `embedding_position`, not a mixer's): the vector with entry 2i = sin(p * theta**(-2i/width)) and
     entry 2i+1 = cos of the same angle is added to the token's embedding.
+    kind 'rope_pairs': the rotation of NEIGHBOURING pairs (2i, 2i+1) of the first rotary_dim entries by the angle
+    position * f_i, f_i = theta**(-2i/rotary_dim); `params` scaling = (factor, original, fast, slow) stretches the
+    frequencies: with pair(t) = rotary_dim * ln(original / (2 pi t)) / (2 ln theta), lo = max(floor(pair(fast)), 0),
+    hi = min(ceil(pair(slow)), rotary_dim - 1) and ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), the frequency
+    is f_i / factor * ramp_i + f_i * (1 - ramp_i); `params` magnitude multiplies cos and sin.
     `params` carries what other kinds need.
     """
     kind: str
@@ -110,6 +116,8 @@ class MixerSpec:
     distance_bias: Optional[Tuple[int, float]] = None
     head_temperature: bool = False
     log_distance_bias: bool = False
+    keep_first: int = 0                    # with a window: the sequence's first so many keys stay visible to every later query
+    softmax_sink: Optional[float] = None   # a score whose exponential joins the softmax's denominator and carries no value
 
 
 @dataclass(frozen=True)
@@ -141,6 +149,9 @@ class BlockSpec:
     plus its causal convolution over time, channel by channel: u_t = h_t + sum_j w[:, j] * h_(t - taps + 1 + j) with
     zeros before the sequence's start (tensors `input_conv_names`, one [hidden, taps] per sublayer; the last taps - 1
     rows of h are kept per request, layer and sublayer).
+    arrangement 'sandwich_norm': h += norm1b(mixer(norm1(h))); h += norm2b(ffn(norm2(h))): a norm in front of each
+    sublayer and one on its output (`mixer_post_norm`, `feed_forward_post_norm`, named `mixer_post_norm_name` and
+    `feed_forward_post_norm_name`).
     `feed_forward` None: a layer that is its mixer only.
     `connections` = (streams, name of the mixer's connection tensors, name of the feed-forward's): each
     sublayer has tensors `<name>.in` [streams], `<name>.out` [streams], `<name>.mix` [streams, streams]; its
@@ -158,6 +169,10 @@ class BlockSpec:
     residual_scale: float = 1.0
     input_conv: Optional[int] = None
     input_conv_names: Tuple[str, str] = ("conv1", "conv2")
+    mixer_post_norm: Optional[NormSpec] = None
+    feed_forward_post_norm: Optional[NormSpec] = None
+    mixer_post_norm_name: str = "post_mixer_layernorm"
+    feed_forward_post_norm_name: str = "post_feed_forward_layernorm"
 
 
 @dataclass(frozen=True)

@@ -36,6 +36,9 @@
 // `value_row_stride` (elements; 0: dv) lets the values be the first dv entries of rows that are wider, e.g. of
 // the key rows themselves: a layer that caches one latent row per token, scores against all of it and sums its
 // first part needs no second tensor.  Value widths above 256 take an instantiation with twice the accumulators.
+// `keep_first` (with a window): the first so many keys of the sequence stay visible to every query behind them,
+// at their true positions; the walk is then over the kept keys below the window and the window itself, as one
+// list.  `has_sink`: one more term exp(sink_score) in the softmax's denominator that carries no value.
 // With `rows` (int32 [num_tokens]) the kernel works on the listed tokens only (a step's single decoded tokens
 // while its prompt portions take a tensor-core kernel); -1 entries pad the list.
 #include "common.cuh"
@@ -57,7 +60,7 @@ __global__ void paged_attention_generic_kernel(
     long long out_stride, int out_off, int vec, int32_t* __restrict__ status,
     const float* __restrict__ dist_bias, int dist_len, int gate_per_head, const int32_t* __restrict__ rows,
     const float* __restrict__ head_scale, const float* __restrict__ log_r1, const float* __restrict__ log_r2,
-    long long value_row_stride) {
+    long long value_row_stride, int keep_first, int has_sink, float sink_score) {
     pdl_begin();
     extern __shared__ float smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -88,9 +91,13 @@ __global__ void paged_attention_generic_kernel(
 #pragma unroll
     for (int r = 0; r < MAXDV / 32; ++r) acc[r] = 0.0f;
 
-    for (int base = lo + 32 * warp; base <= pos; base += 32 * AG_WARPS) {
-        const int j = base + lane;
-        const bool valid = j <= pos;
+    // the keys a query walks: [0, head) kept from the sequence's start, then [lo, pos]
+    const int head = keep_first < lo ? keep_first : lo;
+    const int walk = head + pos - lo + 1;
+    for (int base = 32 * warp; base < walk; base += 32 * AG_WARPS) {
+        const int u0 = base + lane;
+        const int j = u0 < head ? u0 : lo + (u0 - head);
+        const bool valid = u0 < walk;
         long long voff = -1;
         float s = -CUDART_INF_F;
         if (valid) {
@@ -126,7 +133,7 @@ __global__ void paged_attention_generic_kernel(
         m = m_new;
 #pragma unroll
         for (int r = 0; r < MAXDV / 32; ++r) acc[r] *= alpha;
-        const int count = min(32, pos - base + 1);
+        const int count = min(32, walk - base);
         const int regs = (dv + 31) >> 5;               // value entries a lane holds
         for (int jj = 0; jj < count; jj += 4) {       // four keys' value rows in flight: their loads do not wait for one another
             float pj[4];
@@ -168,6 +175,8 @@ __global__ void paged_attention_generic_kernel(
         const float mw = merge[w2 * (dv + 2) + dv];
         if (mw != -CUDART_INF_F) l_all += merge[w2 * (dv + 2) + dv + 1] * expf(mw - m_all);
     }
+    if (has_sink) l_all += expf(sink_score - m_all);   // the sink joins the sum; it has no value row (far above every
+                                                       // score it overflows to infinity and the output to zero: its limit)
     T* orow = out + static_cast<size_t>(t) * out_stride + out_off + static_cast<size_t>(h) * dv;
     const float* grow = gate ? gate + static_cast<size_t>(t) * gate_stride + gate_off +
                                    (gate_per_head ? static_cast<size_t>(h) : static_cast<size_t>(h) * dv) : nullptr;
@@ -193,8 +202,10 @@ extern "C" int llm_paged_attention_generic_kv(
     int num_tokens, int nq, int nkv, int d, int dv, int page_size, int window, float scale, int num_pages,
     const float* gate, long long gate_stride, int gate_off, float out_scale, long long out_stride, int out_off,
     int32_t* status, const float* dist_bias, int dist_len, int gate_per_head, const int32_t* rows,
-    const float* head_scale, const float* log_r1, const float* log_r2, long long value_row_stride, uintptr_t stream) {
+    const float* head_scale, const float* log_r1, const float* log_r2, long long value_row_stride, int keep_first,
+    int has_sink, float sink_score, uintptr_t stream) {
     if (num_tokens <= 0) return LLM_OK;
+    if (keep_first < 0) return LLM_REFUSED_SIZE;
     if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || d <= 0 || d > AG_MAX_DK || dv <= 0 || dv > AG_MAX_DV || page_size <= 0)
         return LLM_REFUSED_SIZE;
     if ((log_r1 == nullptr) != (log_r2 == nullptr) || value_row_stride < 0 || (value_row_stride > 0 && value_row_stride < dv))
@@ -215,7 +226,7 @@ extern "C" int llm_paged_attention_generic_kv(
         static_cast<const TC*>(values), key_page_stride, value_page_stride, positions,             \
         token_entry, entry_slot, block_table, table_stride, num_tokens, nq, nkv, d, dv, page_size, \
         window, scale, num_pages, gate, gate_stride, gate_off, out_scale, out_stride, out_off, vec, status, \
-        dist_bias, dist_len, gate_per_head, rows, head_scale, log_r1, log_r2, value_row_stride)
+        dist_bias, dist_len, gate_per_head, rows, head_scale, log_r1, log_r2, value_row_stride, keep_first, has_sink, sink_score)
     if (dtype == LLM_DT_F32 && cache_dtype == LLM_DT_F32) { LAUNCH(float, float); }
     else if (dtype == LLM_DT_BF16 && cache_dtype == LLM_DT_BF16) { LAUNCH(bf16, bf16); }
     else if (dtype == LLM_DT_F32 && cache_dtype == LLM_DT_BF16) { LAUNCH(float, bf16); }
@@ -242,5 +253,5 @@ extern "C" int llm_paged_attention_generic(
                                           cache_dtype, 2 * half, 2 * half, positions, token_entry, entry_slot,
                                           block_table, table_stride, num_tokens, nq, nkv, d, d, page_size, window,
                                           scale, num_pages, nullptr, 0, 0, 1.0f, static_cast<long long>(nq) * d, 0,
-                                          status, nullptr, 0, 0, nullptr, nullptr, nullptr, nullptr, 0, stream);
+                                          status, nullptr, 0, 0, nullptr, nullptr, nullptr, nullptr, 0, 0, 0, 0.0f, stream);
 }

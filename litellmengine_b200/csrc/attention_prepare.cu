@@ -6,6 +6,10 @@
 //       0  none
 //       1  per head:        x_head * rsqrt(mean(x_head^2) + eps) * w[i mod dk]
 //       2  whole projection: x * rsqrt(mean over ALL heads' entries of x^2 + eps) * w[i]
+//   rotation (optional, after the norm): of the first rot_dims entries of every q and k head, pairs (2i, 2i + 1)
+//       (`rot_pairs` 1) or (i, i + rot_dims/2) (0) turn by the angle float(p) * rot_freq[i]; the pair (a, b) becomes
+//       (a cos - b sin, b cos + a sin) * rot_mag.  `rot_freq` is a float32 table [rot_dims/2] that its owner makes
+//       (any stretching of the frequencies is the owner's); angle, sine and cosine are 32-bit.
 //   query temperature (optional): q *= 1 + coef * ln(floor((p + 1) / every) + 1), p the token's position
 //   q is stored in the compute dtype [T, nq*dk]; k and v go to the token's place in its request's
 //   pages, `keys` [pages, nkv, page, dk] and `values` [pages, nkv, page, dv] (any page strides, so that
@@ -41,7 +45,8 @@ __global__ void attention_prepare_kernel(
     long long key_page_stride, long long value_page_stride,
     const int32_t* __restrict__ positions, const int32_t* __restrict__ token_entry,
     const int32_t* __restrict__ entry_slot, const int32_t* __restrict__ block_table, int table_stride,
-    int nq, int nkv, int dk, int dv, int page_size, int num_pages, int vec, int32_t* __restrict__ status) {
+    int nq, int nkv, int dk, int dv, int page_size, int num_pages, int vec, int32_t* __restrict__ status,
+    const float* __restrict__ rot_freq, int rot_dims, float rot_mag, int rot_pairs) {
     pdl_begin();
     extern __shared__ __align__(16) float smem[];
     const int nqe = nq * dk, nke = nkv * dk, nve = nkv * dv;
@@ -113,6 +118,23 @@ __global__ void attention_prepare_kernel(
     __syncthreads();
 
     const int pos = positions[t];
+    if (rot_freq) {                             // a thread a pair, over the heads of q and then of k
+        const int half = rot_dims >> 1;
+        const int pairs = (nq + (keys ? nkv : 0)) * half;
+        for (int idx = threadIdx.x; idx < pairs; idx += blockDim.x) {
+            const int head = idx / half, i = idx - head * half;
+            float* x = head < nq ? fq + head * dk : fk + (head - nq) * dk;
+            const int ia = rot_pairs ? 2 * i : i, ib = rot_pairs ? 2 * i + 1 : i + half;
+            float sn, cs;
+            sincosf(static_cast<float>(pos) * rot_freq[i], &sn, &cs);
+            sn *= rot_mag;
+            cs *= rot_mag;
+            const float a = x[ia], b = x[ib];
+            x[ia] = a * cs - b * sn;
+            x[ib] = b * cs + a * sn;
+        }
+        __syncthreads();
+    }
     float temp = 1.0f;
     if (temp_every > 0) temp = 1.0f + temp_coef * logf(static_cast<float>((pos + 1) / temp_every + 1));
     TQ* qo = q_out + static_cast<size_t>(t) * nqe;
@@ -162,10 +184,11 @@ extern "C" int llm_attention_prepare(
     void* q_out, int q_dtype, void* keys, void* values, int cache_dtype, long long key_page_stride,
     long long value_page_stride, const int32_t* positions, const int32_t* token_entry, const int32_t* entry_slot,
     const int32_t* block_table, int table_stride, int num_tokens, int nq, int nkv, int dk, int dv, int page_size,
-    int num_pages, int32_t* status, uintptr_t stream) {
+    int num_pages, int32_t* status, const float* rot_freq, int rot_dims, float rot_mag, int rot_pairs, uintptr_t stream) {
     if (num_tokens <= 0) return LLM_OK;
     if (nq <= 0 || nkv < 0 || dk <= 0 || dv <= 0 || norm_scope < 0 || norm_scope > 2 || temp_every < 0)
         return LLM_REFUSED_SIZE;
+    if (rot_freq && (rot_dims <= 0 || rot_dims % 2 || rot_dims > dk)) return LLM_REFUSED_SIZE;
     if (keys && (!values || !block_table || page_size <= 0)) return LLM_REFUSED_SIZE;
     const size_t smem = (static_cast<size_t>(nq) * dk + static_cast<size_t>(nkv) * dk + 33) * sizeof(float);
     if (smem > 200 * 1024) return LLM_REFUSED_SIZE;
@@ -188,7 +211,7 @@ extern "C" int llm_attention_prepare(
                    bk, bv, qw, kw, norm_scope, eps, temp_coef, temp_every, static_cast<TQ*>(q_out),               \
                    static_cast<TC*>(keys), static_cast<TC*>(values), key_page_stride, value_page_stride,          \
                    positions, token_entry, entry_slot, block_table, table_stride, nq, nkv, dk, dv, page_size,     \
-                   num_pages, vec, status);                                                                       \
+                   num_pages, vec, status, rot_freq, rot_dims, rot_mag, rot_pairs);                               \
     } while (0)
     if (q_dtype == LLM_DT_F32 && cache_dtype == LLM_DT_F32) LAUNCH(float, float);
     else if (q_dtype == LLM_DT_BF16 && cache_dtype == LLM_DT_BF16) LAUNCH(bf16, bf16);

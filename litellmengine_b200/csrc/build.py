@@ -27,6 +27,7 @@ CSRC = os.path.dirname(os.path.abspath(__file__))
 FAMILIES: Dict[str, List[str]] = {
     "embedding": ["embedding.cu"],
     "norm": ["norm.cu"],
+    "tanh_norm": ["tanh_norm.cu"],
     "activation": ["activation.cu"],
     "rope_cache": ["rope_cache.cu"],
     "attention_generic": ["attention_generic.cu"],

@@ -24,6 +24,7 @@ _SIGNATURES = {
     "hc_pool_give": ([c_void_p, c_void_p, c_int], c_int),
     "hc_pool_used": ([c_void_p, c_void_p], c_int),
     "hc_cache_new": ([c_int, c_void_p, c_int, c_int, c_int, c_int, c_int], c_void_p),
+    "hc_cache_set_head": ([c_void_p, c_int, c_int], c_int),
     "hc_cache_delete": ([c_void_p], None),
     "hc_cache_pool": ([c_void_p, c_int], c_void_p),
     "hc_cache_table": ([c_void_p, c_int], POINTER(c_int32)),

@@ -75,9 +75,10 @@ struct Pool {
 
 struct Group {
     int page_size, window, max_pages;                    // window < 0: every earlier position stays
+    int head = 0;                                        // with a window: the first `head` positions stay all the same
     Pool pool;
     std::vector<int32_t> table;                          // [slots][max_pages], -1 where nothing is held
-    std::vector<int32_t> first_held, num_logical;        // per slot: lowest logical page still held; pages ever appended
+    std::vector<int32_t> first_held, num_logical;        // per slot: lowest logical page still held (beyond the head's); pages ever appended
     std::vector<int32_t> pending_index, pending_value;   // table entries changed since the last drain
 
     Group(int page_size_, int window_, int num_pages, int slots, int max_pages_)
@@ -108,7 +109,7 @@ struct Group {
         if (window < 0) return HC_OK;
         const long long first_needed = std::max(0LL, length - window + 1);
         const int keep_from = static_cast<int>(std::min<long long>(first_needed / page_size, num_logical[slot]));
-        const int lo = first_held[slot];
+        const int lo = std::max<int>(first_held[slot], pages_for(head));     // the head's pages never go back here
         if (keep_from <= lo) return HC_OK;
         const int rc = pool.give(table.data() + static_cast<size_t>(slot) * max_pages + lo, keep_from - lo);
         if (rc != HC_OK) return rc;
@@ -116,9 +117,15 @@ struct Group {
         *given = keep_from - lo;
         return HC_OK;
     }
+    // The pages of the head that a slot still holds below `first_held`: a trim leaves them where they are.
+    int head_held(int slot) const {
+        const int h = pages_for(head);
+        return first_held[slot] > h ? h : 0;
+    }
     int release(int slot) {
         const int lo = first_held[slot], hi = num_logical[slot];
-        const int rc = pool.give(table.data() + static_cast<size_t>(slot) * max_pages + lo, hi - lo);
+        int rc = pool.give(table.data() + static_cast<size_t>(slot) * max_pages, head_held(slot));
+        if (rc == HC_OK) rc = pool.give(table.data() + static_cast<size_t>(slot) * max_pages + lo, hi - lo);
         if (rc != HC_OK) return rc;
         first_held[slot] = num_logical[slot] = 0;
         return HC_OK;
@@ -252,6 +259,13 @@ void* hc_cache_new(int num_groups, const int32_t* windows, int page_size, int nu
     c->live.assign(max_slots, 0);
     c->length.assign(max_slots, 0);
     return c;
+}
+// Group g keeps the first `head` positions of every request whatever its window (before any request is admitted).
+int hc_cache_set_head(void* c, int g, int head) {
+    Cache* cc = cache_of(c);
+    if (g < 0 || g >= static_cast<int>(cc->groups.size()) || head < 0) return fail(HC_MISUSE, "no such group, or a negative head");
+    cc->groups[g].head = head;
+    return HC_OK;
 }
 void hc_cache_delete(void* c) { delete cache_of(c); }
 void* hc_cache_pool(void* c, int g) { return &cache_of(c)->groups[g].pool; }
@@ -394,7 +408,8 @@ int hc_cache_check(void* cp) {
                     return fail(HC_MISUSE, "group " + str(gi) + ": released slot " + str(slot) + " still has pages");
                 continue;
             }
-            for (int i = g.first_held[slot]; i < g.num_logical[slot]; ++i) {
+            for (int i = 0; i < g.num_logical[slot]; ++i) {
+                if (i >= g.head_held(slot) && i < g.first_held[slot]) continue;      // given back when the window passed
                 const int p = g.table[static_cast<size_t>(slot) * g.max_pages + i];
                 if (p < 0 || p >= g.pool.num_pages) return fail(HC_MISUSE, "group " + str(gi) + ": slot " + str(slot) + " holds page id " + str(p));
                 if (++count[p] > 1) return fail(HC_MISUSE, "group " + str(gi) + ": a page is held twice");

@@ -13,12 +13,25 @@
 //                      product with W_uk), and the rotated q_rot into columns R .. R+P of head h of the packed
 //                      query [T, H*(R+P)], whose first R columns per head that product then fills.
 //
-// Rotation: the first `dims` entries of the P-part, entry i paired with i + dims/2, by the angle
-// float(position) * inv_freq[i], sine and cosine in 32-bit; the rest passes unchanged.  Norms are 32-bit.
+// Rotation: the first `dims` entries of the P-part, entry i paired with i + dims/2 (`rot_pairs` 0) or entry 2i with
+// 2i + 1 (1), by the angle float(position) * inv_freq[i], sine and cosine in 32-bit and both times `rot_mag`; the
+// rest passes unchanged.  Norms are 32-bit.
 #include "common.cuh"
 #include <math_constants.h>
 
 #define LA_THREADS 256
+
+// entry i (< dims) of a rotated part x at position pos
+__device__ __forceinline__ float la_rotated(const float* x, int i, int dims, float pos, const float* inv_freq,
+                                            int rot_pairs, float rot_mag) {
+    const int half = dims / 2;
+    const bool first = rot_pairs ? (i & 1) == 0 : i < half;
+    const int f = rot_pairs ? i >> 1 : (first ? i : i - half);
+    const int other = rot_pairs ? (i ^ 1) : (first ? i + half : i - half);
+    float sn, cs;
+    sincosf(pos * inv_freq[f], &sn, &cs);
+    return (first ? x[i] * cs - x[other] * sn : x[i] * cs + x[other] * sn) * rot_mag;
+}
 
 template <typename TQ, typename TC>
 __global__ void latent_prepare_kernel(
@@ -27,7 +40,7 @@ __global__ void latent_prepare_kernel(
     TQ* __restrict__ cq_out, TC* __restrict__ keys, long long key_page_stride,
     const int32_t* __restrict__ positions, const int32_t* __restrict__ token_entry,
     const int32_t* __restrict__ entry_slot, const int32_t* __restrict__ block_table, int table_stride,
-    int page_size, int num_pages, int32_t* __restrict__ status) {
+    int page_size, int num_pages, int32_t* __restrict__ status, int rot_pairs, float rot_mag) {
     pdl_begin();
     __shared__ float scratch[33];
     const int t = blockIdx.x;
@@ -58,17 +71,8 @@ __global__ void latent_prepare_kernel(
     const float inv = 1.0f / sqrtf(block_sum(ss_kv, scratch) / static_cast<float>(R) + eps);
     for (int i = threadIdx.x; i < R; i += blockDim.x) dst[i] = from_f32<TC>(row[dkv_off + i] * inv * wkv[i]);
     const float* kr = row + dkv_off + R;
-    const int half = dims / 2;
-    for (int i = threadIdx.x; i < P; i += blockDim.x) {
-        float v = kr[i];
-        if (i < dims) {
-            const int f = i < half ? i : i - half;
-            float sn, cs;
-            sincosf(static_cast<float>(pos) * inv_freq[f], &sn, &cs);
-            v = i < half ? kr[i] * cs - kr[i + half] * sn : kr[i] * cs + kr[i - half] * sn;
-        }
-        dst[R + i] = from_f32<TC>(v);
-    }
+    for (int i = threadIdx.x; i < P; i += blockDim.x)
+        dst[R + i] = from_f32<TC>(i < dims ? la_rotated(kr, i, dims, static_cast<float>(pos), inv_freq, rot_pairs, rot_mag) : kr[i]);
 }
 
 extern "C" int llm_latent_prepare(
@@ -76,7 +80,7 @@ extern "C" int llm_latent_prepare(
     const float* wkv, float eps, const float* inv_freq, void* cq_out, int q_dtype, void* keys, int cache_dtype,
     long long key_page_stride, const int32_t* positions, const int32_t* token_entry, const int32_t* entry_slot,
     const int32_t* block_table, int table_stride, int num_tokens, int page_size, int num_pages, int32_t* status,
-    uintptr_t stream) {
+    int rot_pairs, float rot_mag, uintptr_t stream) {
     if (num_tokens <= 0) return LLM_OK;
     if (Q <= 0 || R <= 0 || P < 0 || dims < 0 || dims > P || dims % 2) return LLM_REFUSED_SIZE;
     if (keys && (!block_table || page_size <= 0 || !wkv || (dims > 0 && !inv_freq))) return LLM_REFUSED_SIZE;
@@ -86,7 +90,7 @@ extern "C" int llm_latent_prepare(
     launch_pdl((latent_prepare_kernel<TQ, TC>), dim3(num_tokens), dim3(LA_THREADS), 0, s, proj, proj_stride, dq_off,  \
                dkv_off, Q, R, P, dims, wq, wkv, eps, inv_freq, static_cast<TQ*>(cq_out), static_cast<TC*>(keys),     \
                key_page_stride, positions, token_entry, entry_slot, block_table, table_stride, page_size, num_pages, \
-               status)
+               status, rot_pairs, rot_mag)
     if (q_dtype == LLM_DT_F32 && cache_dtype == LLM_DT_F32) LAUNCH(float, float);
     else if (q_dtype == LLM_DT_BF16 && cache_dtype == LLM_DT_BF16) LAUNCH(bf16, bf16);
     else if (q_dtype == LLM_DT_F32 && cache_dtype == LLM_DT_BF16) LAUNCH(float, bf16);
@@ -100,7 +104,7 @@ extern "C" int llm_latent_prepare(
 template <typename TQ>
 __global__ void latent_q_split_kernel(const float* __restrict__ q, TQ* __restrict__ qn, TQ* __restrict__ packed,
                                       const int32_t* __restrict__ positions, const float* __restrict__ inv_freq,
-                                      int num_tokens, int H, int D, int P, int R, int dims) {
+                                      int num_tokens, int H, int D, int P, int R, int dims, int rot_pairs, float rot_mag) {
     pdl_begin();
     const int t = blockIdx.x, h = blockIdx.y;
     const float* src = q + (static_cast<size_t>(t) * H + h) * (D + P);
@@ -108,23 +112,14 @@ __global__ void latent_q_split_kernel(const float* __restrict__ q, TQ* __restric
     for (int i = threadIdx.x; i < D; i += blockDim.x) n[i] = from_f32<TQ>(src[i]);
     TQ* dst = packed + (static_cast<size_t>(t) * H + h) * (R + P) + R;
     const float* qr = src + D;
-    const int half = dims / 2;
     const float pos = static_cast<float>(positions[t]);
-    for (int i = threadIdx.x; i < P; i += blockDim.x) {
-        float v = qr[i];
-        if (i < dims) {
-            const int f = i < half ? i : i - half;
-            float sn, cs;
-            sincosf(pos * inv_freq[f], &sn, &cs);
-            v = i < half ? qr[i] * cs - qr[i + half] * sn : qr[i] * cs + qr[i - half] * sn;
-        }
-        dst[i] = from_f32<TQ>(v);
-    }
+    for (int i = threadIdx.x; i < P; i += blockDim.x)
+        dst[i] = from_f32<TQ>(i < dims ? la_rotated(qr, i, dims, pos, inv_freq, rot_pairs, rot_mag) : qr[i]);
 }
 
 extern "C" int llm_latent_q_split(const float* q, void* qn, void* packed, int dtype, const int32_t* positions,
                                   const float* inv_freq, int num_tokens, int H, int D, int P, int R, int dims,
-                                  uintptr_t stream) {
+                                  int rot_pairs, float rot_mag, uintptr_t stream) {
     if (num_tokens <= 0) return LLM_OK;
     if (H <= 0 || H > 65535 || D <= 0 || P < 0 || R <= 0 || dims < 0 || dims > P || dims % 2 || (dims > 0 && !inv_freq))
         return LLM_REFUSED_SIZE;
@@ -132,10 +127,10 @@ extern "C" int llm_latent_q_split(const float* q, void* qn, void* packed, int dt
     const int threads = (D > 64 || P > 64) ? 128 : 64;
     if (dtype == LLM_DT_F32)
         launch_pdl((latent_q_split_kernel<float>), dim3(num_tokens, H), dim3(threads), 0, s, q, static_cast<float*>(qn),
-                   static_cast<float*>(packed), positions, inv_freq, num_tokens, H, D, P, R, dims);
+                   static_cast<float*>(packed), positions, inv_freq, num_tokens, H, D, P, R, dims, rot_pairs, rot_mag);
     else if (dtype == LLM_DT_BF16)
         launch_pdl((latent_q_split_kernel<bf16>), dim3(num_tokens, H), dim3(threads), 0, s, q, static_cast<bf16*>(qn),
-                   static_cast<bf16*>(packed), positions, inv_freq, num_tokens, H, D, P, R, dims);
+                   static_cast<bf16*>(packed), positions, inv_freq, num_tokens, H, D, P, R, dims, rot_pairs, rot_mag);
     else
         return LLM_REFUSED_DTYPE;
     return launch_status();

@@ -8,6 +8,15 @@
 //                    chosen (ties go to the lower index); their weights are s / (sum of the chosen s +
 //                    1e-20) * route_scale.  Written as a dense row of float32 weights [experts] (zero for
 //                    experts that were not chosen) and, optionally, as the lists ids [top], weights [top].
+//                    `softmax` 1: the scores are softmax(z) over all router outputs instead.  `correction`
+//                    (float32 [router outputs], optional) is added to a score for the CHOICE only; the weights
+//                    are made of the scores themselves.  The last `identity` router outputs stand for no
+//                    expert at all: a token that picks one gets its own input back times the weight.  Those
+//                    have no column in the dense row (it has E - identity columns), their place in the lists
+//                    holds id -1 and weight 0, and the sum of their weights goes to `idw` [tokens].
+//                    The experts' activation: g = min(gate, limit), u = clamp(up, -limit, limit),
+//                    w * g * sigmoid(alpha g) * (u + up_shift); limit = infinity, alpha = 1, up_shift = 0 is
+//                    the plain silu(gate) * up.
 // moe_act_kernel     from the float32 product [T, experts * 2 * ff] of the token rows with every expert's
 //                    [gate; up] matrix: act[t, e*ff + f] = w[t, e] * g * sigmoid(alpha g) * (u + 1) with
 //                    g = min(gate, limit), u = clamp(up, -limit, limit), in the compute dtype, zero where
@@ -22,7 +31,8 @@
 template <typename TX>
 __global__ void moe_route_kernel(const TX* __restrict__ x, const float* __restrict__ wr, float* __restrict__ dense,
                                  int32_t* __restrict__ ids, float* __restrict__ weights, int num_tokens, int W, int E,
-                                 int top, int groups, int keep, float route_scale, int vec) {
+                                 int top, int groups, int keep, float route_scale, int vec, int softmax,
+                                 const float* __restrict__ correction, int identity, float* __restrict__ idw) {
     pdl_begin();
     extern __shared__ float smem[];
     const int G = groups > 0 ? groups : 1;
@@ -69,25 +79,41 @@ __global__ void moe_route_kernel(const TX* __restrict__ x, const float* __restri
 #pragma unroll
         for (int k = 0; k < MOE_ROUTE_TOKENS; ++k) {
             const float d = warp_sum(dot[k]);
-            if (lane == 0 && k < nt) score[k * E + e] = 1.0f / (1.0f + expf(-d));
+            if (lane == 0 && k < nt) score[k * E + e] = softmax ? d : 1.0f / (1.0f + expf(-d));
         }
     }
     __syncthreads();
+    if (softmax) {                                   // a warp a token: maximum, exponentials, their sum
+        if (warp < nt) {
+            float* sc = score + warp * E;
+            float top_z = -CUDART_INF_F;
+            for (int e = lane; e < E; e += 32) top_z = fmaxf(top_z, sc[e]);
+            top_z = warp_max(top_z);
+            float sum = 0.0f;
+            for (int e = lane; e < E; e += 32) {
+                const float p = expf(sc[e] - top_z);
+                sc[e] = p;
+                sum += p;
+            }
+            sum = warp_sum(sum);
+            for (int e = lane; e < E; e += 32) sc[e] = sc[e] / sum;
+        }
+        __syncthreads();
+    }
     const int per = groups > 0 ? E / groups : E;
     for (int idx = tid; idx < nt * G && groups > 0; idx += blockDim.x) {
         const int k = idx / G, g = idx - k * G;
-        float a = -1.0f, b = -1.0f;                  // the two largest (scores are in (0, 1))
+        float a = -CUDART_INF_F, b = -CUDART_INF_F;  // the two largest
         for (int j = 0; j < per; ++j) {
-            const float sc = score[k * E + g * per + j];
+            const float sc = score[k * E + g * per + j] + (correction ? correction[g * per + j] : 0.0f);
             if (sc > a) { b = a; a = sc; }
             else if (sc > b) b = sc;
         }
         gscore[idx] = per > 1 ? a + b : a;
     }
-    for (int idx = tid; idx < nt * E; idx += blockDim.x) {
-        allowed[idx] = groups > 0 ? 0 : 1;
-        dense[t0 * E + idx] = 0.0f;
-    }
+    const int real = E - identity;                   // the experts that are feed-forwards: the dense row's columns
+    for (int idx = tid; idx < nt * E; idx += blockDim.x) allowed[idx] = groups > 0 ? 0 : 1;
+    for (int idx = tid; idx < nt * real; idx += blockDim.x) dense[t0 * real + idx] = 0.0f;
     __syncthreads();
     if (tid < nt) {                                  // one thread a token walks the choices (a few dozen steps)
         const int k = tid;
@@ -108,31 +134,38 @@ __global__ void moe_route_kernel(const TX* __restrict__ x, const float* __restri
         for (int n = 0; n < top; ++n) {
             int best = -1;
             float bs = -CUDART_INF_F;
-            for (int e = 0; e < E; ++e)
-                if (ok[e] && sc[e] > bs) { bs = sc[e]; best = e; }
+            for (int e = 0; e < E; ++e) {
+                const float cv = sc[e] + (correction ? correction[e] : 0.0f);       // the choice's score; the weight's is sc
+                if (ok[e] && cv > bs) { bs = cv; best = e; }
+            }
             chosen[n] = best;
             if (best >= 0) {
                 ok[best] = 0;
-                total += bs;
+                total += sc[best];
             }
         }
         const float inv = route_scale / (total + 1e-20f);
+        float own = 0.0f;                            // what the token gets of its own input
         for (int n = 0; n < top; ++n) {
             const int e = chosen[n];
             const float w = e >= 0 ? sc[e] * inv : 0.0f;
-            if (e >= 0) dense[t * E + e] = w;
+            const bool expert = e >= 0 && e < real;
+            if (expert) dense[t * real + e] = w;
+            else if (e >= 0) own += w;
             if (ids) {
-                ids[t * top + n] = e;
-                weights[t * top + n] = w;
+                ids[t * top + n] = expert ? e : -1;
+                weights[t * top + n] = expert ? w : 0.0f;
             }
         }
+        if (idw) idw[t] = own;
     }
 }
 
 extern "C" int llm_moe_route(const void* x, int x_dtype, const float* wr, float* dense, int32_t* ids, float* weights,
                              int num_tokens, int W, int E, int top, int groups, int keep, float route_scale,
-                             uintptr_t stream) {
+                             int softmax, const float* correction, int identity, float* idw, uintptr_t stream) {
     if (num_tokens <= 0) return LLM_OK;
+    if (identity < 0 || identity >= E || (identity > 0 && !idw)) return LLM_REFUSED_SIZE;
     if (W <= 0 || E <= 0 || top <= 0 || top > E || top > 64 || groups < 0) return LLM_REFUSED_SIZE;
     if (groups > 0 && (E % groups || keep <= 0 || keep > groups || keep * (E / groups) < top)) return LLM_REFUSED_SIZE;
     const size_t smem = MOE_ROUTE_TOKENS * (static_cast<size_t>(W) + 2 * E + (groups > 0 ? groups : 1)) * sizeof(float);
@@ -149,7 +182,7 @@ extern "C" int llm_moe_route(const void* x, int x_dtype, const float* wr, float*
             if (e != cudaSuccess) return static_cast<int>(e);                                                       \
         }                                                                                                           \
         launch_pdl(kern, grid, dim3(MOE_ROUTE_THREADS), smem, s, static_cast<const TX*>(x), wr, dense, ids, weights,  \
-                   num_tokens, W, E, top, groups, keep, route_scale, vec);                                          \
+                   num_tokens, W, E, top, groups, keep, route_scale, vec, softmax, correction, identity, idw);      \
     } while (0)
     if (x_dtype == LLM_DT_F32) LAUNCH(float);
     else if (x_dtype == LLM_DT_BF16) LAUNCH(bf16);
@@ -158,6 +191,11 @@ extern "C" int llm_moe_route(const void* x, int x_dtype, const float* wr, float*
     return launch_status();
 }
 
+// An expert's activation: the clamped gate through g * sigmoid(alpha g), times the clamped up value plus `shift`.
+__device__ __forceinline__ float moe_activate(float g, float u, float limit, float alpha, float shift) {
+    const float gc = fminf(g, limit), uc = fminf(fmaxf(u, -limit), limit);
+    return (gc / (1.0f + expf(-alpha * gc))) * (uc + shift);
+}
 __device__ __forceinline__ void moe_store4(float* p, const float (&v)[4]) { *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]); }
 __device__ __forceinline__ void moe_store4(bf16* p, const float (&v)[4]) {
     uint2 raw;
@@ -173,7 +211,7 @@ __device__ __forceinline__ void moe_store4(bf16* p, const float (&v)[4]) {
 template <typename TO, int VEC>
 __global__ void moe_act_kernel(const float* __restrict__ gu, int parts, long long part_stride,
                                const float* __restrict__ dense, TO* __restrict__ act, int E, int ff, float limit,
-                               float alpha) {
+                               float alpha, float shift) {
     pdl_begin();
     const long long pair = blockIdx.x;                  // token * E + expert
     const int f = (blockIdx.y * blockDim.x + threadIdx.x) * VEC;
@@ -195,10 +233,7 @@ __global__ void moe_act_kernel(const float* __restrict__ gu, int parts, long lon
             }
         }
 #pragma unroll
-        for (int c = 0; c < VEC; ++c) {
-            const float gc = fminf(g[c], limit), uc = fminf(fmaxf(u[c], -limit), limit);
-            out[c] = w * (gc / (1.0f + expf(-alpha * gc))) * (uc + 1.0f);
-        }
+        for (int c = 0; c < VEC; ++c) out[c] = w * moe_activate(g[c], u[c], limit, alpha, shift);
     }
     TO* o = act + pair * ff + f;
     if (VEC == 4) moe_store4(o, out);
@@ -206,7 +241,8 @@ __global__ void moe_act_kernel(const float* __restrict__ gu, int parts, long lon
 }
 
 extern "C" int llm_moe_act(const float* gu, int parts, long long part_stride, const float* dense, void* act,
-                           int act_dtype, int num_tokens, int E, int ff, float limit, float alpha, uintptr_t stream) {
+                           int act_dtype, int num_tokens, int E, int ff, float limit, float alpha, float shift,
+                           uintptr_t stream) {
     if (num_tokens <= 0) return LLM_OK;
     if (E <= 0 || ff <= 0 || !(limit > 0.0f)) return LLM_REFUSED_SIZE;
     const long long pairs = static_cast<long long>(num_tokens) * E;
@@ -219,7 +255,7 @@ extern "C" int llm_moe_act(const float* gu, int parts, long long part_stride, co
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
 #define LAUNCH(TO, V)                                                                                          \
     launch_pdl((moe_act_kernel<TO, V>), grid, dim3(128), 0, s, gu, parts, part_stride, dense, static_cast<TO*>(act), E, ff, \
-               limit, alpha)
+               limit, alpha, shift)
     if (act_dtype == LLM_DT_F32) { if (vec) LAUNCH(float, 4); else LAUNCH(float, 1); }
     else if (act_dtype == LLM_DT_BF16) { if (vec) LAUNCH(bf16, 4); else LAUNCH(bf16, 1); }
     else return LLM_REFUSED_DTYPE;
@@ -304,7 +340,8 @@ __device__ __forceinline__ float moe_dot(const TW* __restrict__ w, const float* 
 template <typename TX, typename TW, typename TO>
 __global__ void moe_gate_up_sparse_kernel(const TX* __restrict__ x, const TW* __restrict__ wgu,
                                           const int32_t* __restrict__ ids, const float* __restrict__ weights,
-                                          TO* __restrict__ act, int W, int ff, int top, float limit, float alpha, int vec) {
+                                          TO* __restrict__ act, int W, int ff, int top, float limit, float alpha, int vec,
+                                          float shift) {
     pdl_begin();
     extern __shared__ __align__(16) float xs[];        // [W]
     const int pair = blockIdx.x, t = pair / top;
@@ -320,9 +357,7 @@ __global__ void moe_gate_up_sparse_kernel(const TX* __restrict__ x, const TW* __
             const TW* gr = wgu + (static_cast<size_t>(e) * 2 * ff + f) * W;
             float g, u;
             moe_dot2(gr, gr + static_cast<size_t>(ff) * W, xs, W, lane, vec, g, u);
-            g = fminf(g, limit);
-            u = fminf(fmaxf(u, -limit), limit);
-            out = wt * (g / (1.0f + expf(-alpha * g))) * (u + 1.0f);
+            out = wt * moe_activate(g, u, limit, alpha, shift);
         }
         if (lane == 0) act[static_cast<size_t>(pair) * ff + f] = from_f32<TO>(out);
     }
@@ -352,7 +387,7 @@ __global__ void moe_down_sparse_kernel(const TA* __restrict__ act, const TW* __r
 
 extern "C" int llm_moe_sparse(const void* x, int x_dtype, const void* wgu, const void* wd, int w_dtype, const int32_t* ids,
                               const float* weights, void* act, float* out, int num_tokens, int W, int ff, int E, int top,
-                              float limit, float alpha, uintptr_t stream) {
+                              float limit, float alpha, float shift, uintptr_t stream) {
     if (num_tokens <= 0) return LLM_OK;
     if (W <= 0 || ff <= 0 || E <= 0 || top <= 0 || !(limit > 0.0f)) return LLM_REFUSED_SIZE;
     const size_t smem_a = static_cast<size_t>(W) * sizeof(float), smem_b = static_cast<size_t>(top) * ff * sizeof(float);
@@ -365,12 +400,12 @@ extern "C" int llm_moe_sparse(const void* x, int x_dtype, const void* wgu, const
     const dim3 block(MOE_SPARSE_WARPS * 32);
     if (x_dtype == LLM_DT_F32) {
         launch_pdl((moe_gate_up_sparse_kernel<float, float, float>), grid_a, block, smem_a, s, static_cast<const float*>(x),
-                   static_cast<const float*>(wgu), ids, weights, static_cast<float*>(act), W, ff, top, limit, alpha, vec);
+                   static_cast<const float*>(wgu), ids, weights, static_cast<float*>(act), W, ff, top, limit, alpha, vec, shift);
         launch_pdl((moe_down_sparse_kernel<float, float>), grid_b, block, smem_b, s, static_cast<const float*>(act),
                    static_cast<const float*>(wd), ids, out, W, ff, top, E, vec);
     } else if (x_dtype == LLM_DT_BF16) {
         launch_pdl((moe_gate_up_sparse_kernel<bf16, bf16, bf16>), grid_a, block, smem_a, s, static_cast<const bf16*>(x),
-                   static_cast<const bf16*>(wgu), ids, weights, static_cast<bf16*>(act), W, ff, top, limit, alpha, vec);
+                   static_cast<const bf16*>(wgu), ids, weights, static_cast<bf16*>(act), W, ff, top, limit, alpha, vec, shift);
         launch_pdl((moe_down_sparse_kernel<bf16, bf16>), grid_b, block, smem_b, s, static_cast<const bf16*>(act),
                    static_cast<const bf16*>(wd), ids, out, W, ff, top, E, vec);
     } else {
@@ -441,7 +476,7 @@ __global__ void moe_gather_kernel(const T* __restrict__ x, const int32_t* __rest
 template <typename T>
 __global__ void moe_act_pairs_kernel(const T* __restrict__ gu, const int32_t* __restrict__ row_pair,
                                      const float* __restrict__ weights, T* __restrict__ act, int ff, float limit,
-                                     float alpha, int vec) {
+                                     float alpha, int vec, float shift) {
     pdl_begin();
     const long long r = blockIdx.x;
     const float w = weights[row_pair[r]];
@@ -453,16 +488,12 @@ __global__ void moe_act_pairs_kernel(const T* __restrict__ gu, const int32_t* __
             load8(g + f, a);
             load8(g + ff + f, b);
 #pragma unroll
-            for (int c = 0; c < 8; ++c) {
-                const float gc = fminf(a[c], limit), uc = fminf(fmaxf(b[c], -limit), limit);
-                a[c] = w * (gc / (1.0f + expf(-alpha * gc))) * (uc + 1.0f);
-            }
+            for (int c = 0; c < 8; ++c) a[c] = w * moe_activate(a[c], b[c], limit, alpha, shift);
             store8(o + f, a);
         }
     } else {
         for (int f = blockIdx.y * blockDim.x + threadIdx.x; f < ff; f += gridDim.y * blockDim.x) {
-            const float gc = fminf(to_f32(g[f]), limit), uc = fminf(fmaxf(to_f32(g[ff + f]), -limit), limit);
-            o[f] = from_f32<T>(w * (gc / (1.0f + expf(-alpha * gc))) * (uc + 1.0f));
+            o[f] = from_f32<T>(w * moe_activate(to_f32(g[f]), to_f32(g[ff + f]), limit, alpha, shift));
         }
     }
 }
@@ -509,7 +540,7 @@ extern "C" int llm_moe_sort(const int32_t* ids, int pairs, int E, int32_t* offs,
 // which = 0: gather (a = x [T, W], out = xs [pairs, W]); 1: activation (a = gu [pairs, 2 n], out = act [pairs, n]);
 // 2: combine (a = y [pairs, n], out = float32 [T, n], index = pos).  n is the row width of `out`.
 extern "C" int llm_moe_rows(int which, const void* a, int dtype, const int32_t* index, const float* weights, void* out,
-                            int rows, int n, int top, float limit, float alpha, uintptr_t stream) {
+                            int rows, int n, int top, float limit, float alpha, float shift, uintptr_t stream) {
     if (rows <= 0) return LLM_OK;
     if (n <= 0 || top <= 0 || which < 0 || which > 2) return LLM_REFUSED_SIZE;
     const int esz = dtype == LLM_DT_F32 ? 4 : 2;
@@ -525,9 +556,9 @@ extern "C" int llm_moe_rows(int which, const void* a, int dtype, const int32_t* 
         else return LLM_REFUSED_DTYPE;
     } else if (which == 1) {
         if (dtype == LLM_DT_F32) launch_pdl((moe_act_pairs_kernel<float>), grid, block, 0, s, static_cast<const float*>(a), index,
-                                            weights, static_cast<float*>(out), n, limit, alpha, vec);
+                                            weights, static_cast<float*>(out), n, limit, alpha, vec, shift);
         else if (dtype == LLM_DT_BF16) launch_pdl((moe_act_pairs_kernel<bf16>), grid, block, 0, s, static_cast<const bf16*>(a),
-                                                  index, weights, static_cast<bf16*>(out), n, limit, alpha, vec);
+                                                  index, weights, static_cast<bf16*>(out), n, limit, alpha, vec, shift);
         else return LLM_REFUSED_DTYPE;
     } else {
         if (dtype == LLM_DT_F32) launch_pdl((moe_combine_kernel<float>), grid, block, 0, s, static_cast<const float*>(a), index,
@@ -536,5 +567,43 @@ extern "C" int llm_moe_rows(int which, const void* a, int dtype, const int32_t* 
                                                   static_cast<float*>(out), n, top, vec);
         else return LLM_REFUSED_DTYPE;
     }
+    return launch_status();
+}
+
+// What a routed feed-forward adds beside its experts' weighted sum: out[t] += idw[t] * x[t] (the share of a token's
+// own input, for models whose router may pick "no expert") + shared[t] (an expert that every token runs), in 32-bit.
+// `shared` may come as the `parts` k-splits of a product, `part_stride` floats apart.
+template <typename TX>
+__global__ void moe_finish_kernel(float* __restrict__ out, const TX* __restrict__ x, const float* __restrict__ idw,
+                                  const float* __restrict__ shared, int parts, long long part_stride, long long total, int W) {
+    pdl_begin();
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        float v = out[i];
+        if (idw) v += idw[i / W] * to_f32(x[i]);
+        if (shared)
+            for (int k = 0; k < parts; ++k) v += shared[k * part_stride + i];
+        out[i] = v;
+    }
+}
+
+extern "C" int llm_moe_finish(float* out, const void* x, int x_dtype, const float* idw, const float* shared, int parts,
+                              long long part_stride, int num_tokens, int W, uintptr_t stream) {
+    if (num_tokens <= 0) return LLM_OK;
+    if (W <= 0 || (idw && !x)) return LLM_REFUSED_SIZE;
+    const long long total = static_cast<long long>(num_tokens) * W;
+    const int threads = 256;
+    const long long want = (total + threads - 1) / threads;
+    const dim3 grid(static_cast<unsigned>(want < 4096 ? want : 4096));
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    if (parts < 1) parts = 1;
+    if (x_dtype == LLM_DT_F32)
+        launch_pdl((moe_finish_kernel<float>), grid, dim3(threads), 0, s, out, static_cast<const float*>(x), idw, shared, parts,
+                   part_stride, total, W);
+    else if (x_dtype == LLM_DT_BF16)
+        launch_pdl((moe_finish_kernel<bf16>), grid, dim3(threads), 0, s, out, static_cast<const bf16*>(x), idw, shared, parts,
+                   part_stride, total, W);
+    else
+        return LLM_REFUSED_DTYPE;
     return launch_status();
 }

@@ -244,6 +244,43 @@ def rmsnorm_add(h: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: flo
     return copy
 
 
+def tanh_norm(h: torch.Tensor, y, post, pre, out_dtype: Optional[torch.dtype] = None,
+              rows: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    """The elementwise norm n(v) = tanh(alpha v) * w + b around a residual add, in 32-bit: v = h + post(y) (written back
+    into the float32 stream h unless `rows` picks rows), returned as pre(v) in `out_dtype`.  `post` and `pre` are
+    (alpha float32 [1], w float32 [H], b float32 [H]) or None: without `post`, y joins as it is; without `pre`, nothing
+    is returned.  y: None, a matrix [T, H] (float32 or bfloat16), or a `PartialSum` whose k-splits are added as they
+    are read."""
+    parts, part_stride = 1, 0
+    if isinstance(y, PartialSum):
+        parts, part_stride = y.parts.shape[0], y.parts.stride(0)
+        y = y.parts[0]
+    _dev(h, rows)
+    _i32(rows, "rows")
+    if h.dtype != torch.float32 or h.dim() != 2 or not h.is_contiguous():
+        raise KernelError("tanh_norm wants a contiguous float32 stream [T, H]")
+    T, H = h.shape
+    if y is not None and (not y.is_cuda or tuple(y.shape) != (T, H) or y.stride(1) != 1):
+        raise KernelError("y must be a CUDA matrix of the stream's shape with unit stride along its rows")
+    for norm in (post, pre):
+        if norm is not None:
+            a, w, b = norm
+            _dev(a, w, b)
+            if any(t.dtype != torch.float32 for t in (a, w, b)) or a.numel() != 1 or w.numel() != H or b.numel() != H:
+                raise KernelError("a tanh norm is (alpha [1], weight [H], bias [H]) in float32")
+    n = rows.numel() if rows is not None else T
+    out = torch.empty((n, H), dtype=out_dtype, device=h.device) if pre is not None else None
+    pa, pw, pb = post if post is not None else (None, None, None)
+    na, nw, nb = pre if pre is not None else (None, None, None)
+    f = _fn("tanh_norm", "llm_tanh_norm",
+            [c_void_p, c_void_p, c_int, c_longlong, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+             c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p])
+    _check(f(_ptr(h), _ptr(y), _dt(y) if y is not None else 0, y.stride(0) if y is not None else 0, parts, part_stride,
+             _ptr(pa), _ptr(pw), _ptr(pb), _ptr(na), _ptr(nw), _ptr(nb), _ptr(out), _dt(out) if out is not None else 0,
+             _ptr(rows), n, H, _stream()), "tanh_norm")
+    return out
+
+
 ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
 
 
@@ -430,14 +467,16 @@ def attention_prepare(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, bi
                       norm_scope, eps: float, temperature, keys: Optional[torch.Tensor],
                       values: Optional[torch.Tensor], positions, token_entry, entry_slot,
                       block_table: Optional[torch.Tensor], nq: int, nkv: int, dk: int, dv: int, page_size: int,
-                      status: torch.Tensor, q_dtype: torch.dtype) -> torch.Tensor:
+                      status: torch.Tensor, q_dtype: torch.dtype, rotation=None) -> torch.Tensor:
     """From a float32 projection [T, n] whose columns hold q (from q_off), k (from k_off) and v (from v_off):
     add the biases (`biases` = (bq, bk, bv), any of them None), normalise q and k in 32-bit (`norm_scope`
     'head': each head by itself with a weight [dk]; 'projection': all heads of a token together with a
     weight over the whole projection; None), multiply q by the query temperature 1 + coef * ln(floor((p + 1)
     / every) + 1) (`temperature` = (coef, every) or None), return q [T, nq*dk] in `q_dtype` and write k and
     v into the token's place in `keys` [pages, nkv, page, dk] and `values` [pages, nkv, page, dv] (views
-    with any page stride).  keys None: a mixer that writes no keys and values."""
+    with any page stride).  keys None: a mixer that writes no keys and values.  `rotation` = (freq, dims, mag,
+    pairs): after the norm the first `dims` entries of every q and k head turn by position * freq[i] (float32
+    [dims / 2]), pairs of neighbours (2i, 2i + 1) if `pairs` else (i, i + dims / 2), sine and cosine times `mag`."""
     if proj.dtype != torch.float32 or proj.dim() != 2 or proj.stride(1) != 1 or not proj.is_cuda:
         raise KernelError("proj must be a float32 CUDA matrix with unit stride along its rows")
     bq, bk, bv = biases if biases is not None else (None, None, None)
@@ -462,16 +501,21 @@ def attention_prepare(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, bi
             raise KernelError("keys and values must share a dtype and come with a block table")
         kps, vps, pages = keys.stride(0), values.stride(0), keys.shape[0]
     coef, every = (float(temperature[0]), int(temperature[1])) if temperature is not None else (0.0, 0)
+    freq, rot_dims, rot_mag, rot_pairs = rotation if rotation is not None else (None, 0, 1.0, False)
+    if freq is not None and (not freq.is_cuda or freq.dtype != torch.float32 or freq.numel() != rot_dims // 2):
+        raise KernelError("the rotation's frequencies must be float32 [dims / 2] on the device")
     q = torch.empty((T, nq * dk), dtype=q_dtype, device=proj.device)
     f = _fn("attention_prepare", "llm_attention_prepare",
             [c_void_p, c_longlong, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float,
              c_float, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_longlong, c_longlong, c_void_p, c_void_p,
-             c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+             c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_float,
+             c_int, c_void_p])
     _check(f(_ptr(proj), proj.stride(0), q_off, k_off, v_off, _ptr(bq), _ptr(bk), _ptr(bv), _ptr(q_norm_w),
              _ptr(k_norm_w), scope, float(eps), coef, every, _ptr(q), _dt(q), _ptr(keys), _ptr(values),
              _dt(keys) if keys is not None else 0, kps, vps, _ptr(positions), _ptr(token_entry), _ptr(entry_slot),
              _ptr(block_table), block_table.shape[1] if block_table is not None else 0, T, nq, nkv, dk, dv, page_size,
-             pages, _ptr(status), _stream()), "attention_prepare")
+             pages, _ptr(status), _ptr(freq), int(rot_dims), float(rot_mag), 1 if rot_pairs else 0, _stream()),
+           "attention_prepare")
     return q
 
 
@@ -500,7 +544,8 @@ def paged_attention_generic_kv(q: torch.Tensor, keys: torch.Tensor, values: torc
                                gate_off: int = 0, out_scale: float = 1.0, dist_bias: Optional[torch.Tensor] = None,
                                gate_per_head: bool = False, rows: Optional[torch.Tensor] = None,
                                head_scale: Optional[torch.Tensor] = None, log_bias=None,
-                               values_in_keys: bool = False) -> torch.Tensor:
+                               values_in_keys: bool = False, keep_first: int = 0,
+                               sink: Optional[float] = None) -> torch.Tensor:
     """Causal attention of every token in q [T, nq*dk] over its request's pages of `keys` [pages, nkv, page,
     dk] and `values` [pages, nkv, page, dv] (views with any page stride), written into columns out_off ..
     out_off + nq*dv of `out`, times sigmoid(gate[:, gate_off + ...]) (float32, optional; one value per output
@@ -508,7 +553,9 @@ def paged_attention_generic_kv(q: torch.Tensor, keys: torch.Tensor, values: torc
     len - 1) is added to the scaled scores of query i and key j.  `rows` (int32): only these tokens are worked on
     (-1 entries are padding).  `head_scale` (float32 [nq]) multiplies each head's scaled scores; `log_bias` = (r1, r2),
     float32 [nq] each, takes r1[h] * ln(1 + r2[h] * (i - j)) off them.  `values_in_keys`: `values` is None and the
-    values are the first dv entries of the key rows."""
+    values are the first dv entries of the key rows.  `keep_first`: with a window, the sequence's first so many keys
+    stay visible to every later query.  `sink`: a score whose exponential joins the softmax's denominator without a
+    value (None: ordinary softmax)."""
     r1, r2 = log_bias if log_bias is not None else (None, None)
     _dev(q, positions, token_entry, entry_slot, block_table, status, dist_bias, rows, head_scale, r1, r2)
     _i32(rows, "rows")
@@ -535,14 +582,15 @@ def paged_attention_generic_kv(q: torch.Tensor, keys: torch.Tensor, values: torc
             [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_longlong, c_longlong, c_void_p, c_void_p, c_void_p,
              c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_longlong,
              c_int, c_float, c_longlong, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
-             c_longlong, c_void_p])
+             c_longlong, c_int, c_int, c_float, c_void_p])
     _check(f(_ptr(q), _ptr(out), _dt(q), _ptr(keys), _ptr(values), _dt(keys), keys.stride(0), values.stride(0),
              _ptr(positions), _ptr(token_entry), _ptr(entry_slot), _ptr(block_table), block_table.shape[1],
              rows.numel() if rows is not None else T, nq, nkv,
              dk, dv, page_size, int(window) if window else 0, float(scale), keys.shape[0], _ptr(gate),
              gate.stride(0) if gate is not None else 0, gate_off, float(out_scale), out.stride(0), out_off,
              _ptr(status), _ptr(dist_bias), dist_bias.shape[0] if dist_bias is not None else 0,
-             1 if gate_per_head else 0, _ptr(rows), _ptr(head_scale), _ptr(r1), _ptr(r2), value_row, _stream()),
+             1 if gate_per_head else 0, _ptr(rows), _ptr(head_scale), _ptr(r1), _ptr(r2), value_row,
+             int(keep_first) if window else 0, 0 if sink is None else 1, float(sink or 0.0), _stream()),
            "paged_attention_generic_kv")
     return out
 
@@ -609,11 +657,12 @@ def scaled_add_norm(x: torch.Tensor, y, weight: torch.Tensor, alpha: float, eps:
 def latent_prepare(proj: torch.Tensor, dq_off: int, dkv_off: int, Q: int, R: int, P: int, dims: int, wq: torch.Tensor,
                    wkv: Optional[torch.Tensor], eps: float, inv_freq: Optional[torch.Tensor], keys: Optional[torch.Tensor],
                    batch, block_table: Optional[torch.Tensor], page_size: int, status: torch.Tensor,
-                   q_dtype: torch.dtype) -> torch.Tensor:
+                   q_dtype: torch.dtype, rot_pairs: bool = False, rot_mag: float = 1.0) -> torch.Tensor:
     """From the float32 projection [T, n] with the query latent in columns dq_off .. + Q and (if `keys`) the key/value
     latent and the shared key part in columns dkv_off .. + R + P: returns rmsnorm(query latent) * wq as [T, Q] in
     `q_dtype` and writes [rmsnorm(latent) * wkv | rotated key part] into the token's row of `keys` [pages, 1, page, R +
-    P].  The rotation turns the first `dims` entries of the key part (half-split pairs) by position * inv_freq."""
+    P].  The rotation turns the first `dims` entries of the key part (half-split pairs, or with `rot_pairs` neighbours
+    2i and 2i + 1) by position * inv_freq, sine and cosine times `rot_mag`."""
     if proj.dtype != torch.float32 or proj.dim() != 2 or proj.stride(1) != 1 or not proj.is_cuda:
         raise KernelError("proj must be a float32 CUDA matrix with unit stride along its rows")
     _dev(wq, wkv, inv_freq, batch.positions, batch.token_entry, batch.entry_slot, block_table, status)
@@ -634,17 +683,18 @@ def latent_prepare(proj: torch.Tensor, dq_off: int, dkv_off: int, Q: int, R: int
     f = _fn("latent_attention", "llm_latent_prepare",
             [c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float, c_void_p, c_void_p,
              c_int, c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p,
-             c_void_p])
+             c_int, c_float, c_void_p])
     _check(f(_ptr(proj), proj.stride(0), dq_off, dkv_off, Q, R, P, dims, _ptr(wq), _ptr(wkv), float(eps), _ptr(inv_freq),
              _ptr(cq), _dt(cq), _ptr(keys), _dt(keys) if keys is not None else 0, kps, _ptr(batch.positions),
              _ptr(batch.token_entry), _ptr(batch.entry_slot), _ptr(block_table),
-             block_table.shape[1] if block_table is not None else 0, T, page_size, pages, _ptr(status), _stream()),
+             block_table.shape[1] if block_table is not None else 0, T, page_size, pages, _ptr(status),
+             1 if rot_pairs else 0, float(rot_mag), _stream()),
            "latent_prepare")
     return cq
 
 
 def latent_q_split(q: torch.Tensor, positions: torch.Tensor, inv_freq: Optional[torch.Tensor], H: int, D: int, P: int,
-                   R: int, dims: int, dtype: torch.dtype):
+                   R: int, dims: int, dtype: torch.dtype, rot_pairs: bool = False, rot_mag: float = 1.0):
     """q: float32 [T, H * (D + P)], per head [D unrotated | P to rotate].  Returns (qn [H, T, D] in `dtype`, the
     unrotated parts head-major; packed [T, H * (R + P)] in `dtype` whose columns R .. R + P of every head hold the
     rotated parts and whose first R columns per head are left for the caller to fill)."""
@@ -655,8 +705,10 @@ def latent_q_split(q: torch.Tensor, positions: torch.Tensor, inv_freq: Optional[
     qn = torch.empty((H, T, D), dtype=dtype, device=q.device)
     packed = torch.empty((T, H * (R + P)), dtype=dtype, device=q.device)
     f = _fn("latent_attention", "llm_latent_q_split",
-            [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
-    _check(f(_ptr(q), _ptr(qn), _ptr(packed), _dt(qn), _ptr(positions), _ptr(inv_freq), T, H, D, P, R, dims, _stream()),
+            [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
+             c_void_p])
+    _check(f(_ptr(q), _ptr(qn), _ptr(packed), _dt(qn), _ptr(positions), _ptr(inv_freq), T, H, D, P, R, dims,
+             1 if rot_pairs else 0, float(rot_mag), _stream()),
            "latent_q_split")
     return qn, packed
 
@@ -932,30 +984,63 @@ def stream_norm(streams: torch.Tensor, y, mix: Optional[torch.Tensor], outw: Opt
 
 
 # ---- routed experts ----------------------------------------------------------------------------------------
-def moe_route(x: torch.Tensor, w_router: torch.Tensor, top: int, groups, route_scale: float, lists: bool = False):
-    """Per token of x [T, W]: sigmoid scores of `w_router` (float32 [E, W]), the `top` best among the experts of
-    the best groups (`groups` = (count, keep) or None), weights normalised and scaled.  Returns the dense float32
-    weights [T, E] (zero where not chosen) and, with `lists`, ids int32 [T, top] and weights float32 [T, top]."""
-    _dev(x, w_router)
+def moe_route(x: torch.Tensor, w_router: torch.Tensor, top: int, groups, route_scale: float, lists: bool = False,
+              score: str = "sigmoid", correction: Optional[torch.Tensor] = None, identity: int = 0):
+    """Per token of x [T, W]: scores of `w_router` (float32 [E, W]; `score` 'sigmoid', or 'softmax' over all E), the
+    `top` best among the experts of the best groups (`groups` = (count, keep) or None), weights normalised and
+    scaled.  `correction` (float32 [E]) is added to the scores for the choice only.  The last `identity` router
+    outputs are no experts: a token that picks one gets its own input back times the weight.  Returns the dense
+    float32 weights [T, E - identity] (zero where not chosen) and, with `lists`, ids int32 [T, top] (-1 for an
+    identity pick) and weights float32 [T, top]; with `identity`, also the float32 [T] share of a token's own input."""
+    _dev(x, w_router, correction)
     T, W = x.shape
     E = w_router.shape[0]
     if w_router.dtype != torch.float32 or w_router.shape[1] != W:
         raise KernelError("the router's matrix must be float32 [experts, hidden]")
-    dense = torch.empty((T, E), dtype=torch.float32, device=x.device)
+    if correction is not None and (correction.dtype != torch.float32 or correction.numel() != E):
+        raise KernelError("the router's correction must be float32 [router outputs]")
+    if score not in ("sigmoid", "softmax") or not 0 <= identity < E:
+        raise KernelError("score 'sigmoid' or 'softmax'; identity outputs fewer than the router's")
+    dense = torch.empty((T, E - identity), dtype=torch.float32, device=x.device)
+    idw = torch.empty((T,), dtype=torch.float32, device=x.device) if identity else None
     ids = torch.empty((T, top), dtype=torch.int32, device=x.device) if lists else None
     wts = torch.empty((T, top), dtype=torch.float32, device=x.device) if lists else None
     count, keep = groups if groups is not None else (0, 0)
     f = _fn("moe", "llm_moe_route",
             [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
-             c_void_p])
+             c_int, c_void_p, c_int, c_void_p, c_void_p])
     _check(f(_ptr(x), _dt(x), _ptr(w_router), _ptr(dense), _ptr(ids), _ptr(wts), T, W, E, top, count, keep,
-             float(route_scale), _stream()), "moe_route")
-    return (dense, ids, wts) if lists else dense
+             float(route_scale), 1 if score == "softmax" else 0, _ptr(correction), identity, _ptr(idw), _stream()), "moe_route")
+    out = (dense, ids, wts) if lists else dense
+    if identity:
+        return (out + (idw,)) if lists else (out, idw)
+    return out
+
+
+def moe_finish(out: torch.Tensor, x: Optional[torch.Tensor], idw: Optional[torch.Tensor], shared=None) -> torch.Tensor:
+    """out (float32 [T, W], in place) += idw[t] * x[t] + shared[t]: a token's share of its own input (`idw` float32 [T]
+    with x [T, W], or None) and the output of an expert that every token runs (float32 [T, W], a `PartialSum` or None)."""
+    parts, part_stride = 1, 0
+    if isinstance(shared, PartialSum):
+        parts, part_stride = shared.parts.shape[0], shared.parts.stride(0)
+        shared = shared.parts[0]
+    _dev(out, x, idw, shared)
+    T, W = out.shape
+    if out.dtype != torch.float32 or not out.is_contiguous():
+        raise KernelError("moe_finish wants a contiguous float32 sum")
+    if idw is not None and (x is None or tuple(x.shape) != (T, W) or not x.is_contiguous() or idw.dtype != torch.float32 or idw.numel() != T):
+        raise KernelError("moe_finish: x [T, W] and float32 weights [T]")
+    if shared is not None and (shared.dtype != torch.float32 or tuple(shared.shape) != (T, W) or not shared.is_contiguous()):
+        raise KernelError("moe_finish: the shared expert's output must be float32 [T, W]")
+    f = _fn("moe", "llm_moe_finish", [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_longlong, c_int, c_int, c_void_p])
+    _check(f(_ptr(out), _ptr(x) if idw is not None else None, _dt(x) if idw is not None else 0, _ptr(idw), _ptr(shared), parts,
+             part_stride, T, W, _stream()), "moe_finish")
+    return out
 
 
 def moe_act(gate_up, dense: torch.Tensor, E: int, ff: int, limit: float, alpha: float,
-            out_dtype: torch.dtype) -> torch.Tensor:
-    """act [T, E*ff] = dense[t, e] * g * sigmoid(alpha g) * (u + 1), g = min(gate, limit), u = clamp(up, +-limit),
+            out_dtype: torch.dtype, shift: float = 1.0) -> torch.Tensor:
+    """act [T, E*ff] = dense[t, e] * g * sigmoid(alpha g) * (u + shift), g = min(gate, limit), u = clamp(up, +-limit),
     from the float32 product [T, E*2*ff] (per expert: ff gate columns, then ff up columns; may be a `PartialSum`)."""
     parts, part_stride = 1, 0
     if isinstance(gate_up, PartialSum):
@@ -967,14 +1052,14 @@ def moe_act(gate_up, dense: torch.Tensor, E: int, ff: int, limit: float, alpha: 
         raise KernelError("moe_act wants the float32 product [T, experts * 2 * ff] and the weights [T, experts]")
     act = torch.empty((T, E * ff), dtype=out_dtype, device=gate_up.device)
     f = _fn("moe", "llm_moe_act",
-            [c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p])
+            [c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_float, c_void_p])
     _check(f(_ptr(gate_up), parts, part_stride, _ptr(dense), _ptr(act), _dt(act), T, E, ff, float(limit), float(alpha),
-             _stream()), "moe_act")
+             float(shift), _stream()), "moe_act")
     return act
 
 
 def moe_sparse(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor,
-               ff: int, limit: float, alpha: float) -> torch.Tensor:
+               ff: int, limit: float, alpha: float, shift: float = 1.0) -> torch.Tensor:
     """The routed feed-forward for steps of few tokens: only the chosen experts' matrices are read.  x [T, W] and
     the matrices in one dtype (bfloat16 or float32); `ids`, `weights` [T, top] from `moe_route`.  Returns the
     float32 sum [T, W] of the chosen experts' weighted outputs."""
@@ -990,9 +1075,9 @@ def moe_sparse(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, i
     out = torch.empty((T, W), dtype=torch.float32, device=x.device)
     f = _fn("moe", "llm_moe_sparse",
             [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-             c_int, c_float, c_float, c_void_p])
+             c_int, c_float, c_float, c_float, c_void_p])
     code = f(_ptr(x), _dt(x), _ptr(w_gate_up), _ptr(w_down), _dt(w_down), _ptr(ids), _ptr(weights), _ptr(act), _ptr(out),
-             T, W, ff, E, top, float(limit), float(alpha), _stream())
+             T, W, ff, E, top, float(limit), float(alpha), float(shift), _stream())
     _check(code, "moe_sparse")
     global launch_count
     launch_count += 1                      # two kernels in one call
@@ -1005,7 +1090,7 @@ def grouped_product_available() -> bool:
 
 
 def moe_sorted(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor,
-               E: int, ff: int, limit: float, alpha: float) -> torch.Tensor:
+               E: int, ff: int, limit: float, alpha: float, shift: float = 1.0) -> torch.Tensor:
     """The routed feed-forward for prompt portions: the (token, choice) pairs are sorted by expert (the engine's
     kernels), each expert's rows go through ITS matrices in the library's grouped matrix product (bfloat16 in,
     bfloat16 out, 32-bit accumulation; the row offsets stay on the device), the activation takes each row's
@@ -1017,20 +1102,20 @@ def moe_sorted(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, i
     dev = x.device
     offs = torch.empty(E, dtype=torch.int32, device=dev)
     pos = torch.empty(pairs, dtype=torch.int32, device=dev)
-    row_pair = torch.empty(pairs, dtype=torch.int32, device=dev)
+    row_pair = torch.zeros(pairs, dtype=torch.int32, device=dev)      # rows no pair takes (a pick without an expert) read token 0
     _check(_fn("moe", "llm_moe_sort", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p])(
         _ptr(ids), pairs, E, _ptr(offs), _ptr(pos), _ptr(row_pair), _stream()), "moe_sort")
     rows_fn = _fn("moe", "llm_moe_rows",
-                  [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_float, c_void_p])
+                  [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_float, c_float, c_void_p])
     xs = torch.empty((pairs, W), dtype=x.dtype, device=dev)
-    _check(rows_fn(0, _ptr(x), _dt(x), _ptr(row_pair), None, _ptr(xs), pairs, W, top, 0.0, 0.0, _stream()), "moe_gather")
+    _check(rows_fn(0, _ptr(x), _dt(x), _ptr(row_pair), None, _ptr(xs), pairs, W, top, 0.0, 0.0, 0.0, _stream()), "moe_gather")
     gu = torch._grouped_mm(xs, w_gate_up.view(E, 2 * ff, W).transpose(1, 2), offs=offs)
     act = torch.empty((pairs, ff), dtype=x.dtype, device=dev)
     _check(rows_fn(1, _ptr(gu), _dt(gu), _ptr(row_pair), _ptr(weights), _ptr(act), pairs, ff, top, float(limit), float(alpha),
-                   _stream()), "moe_act_pairs")
+                   float(shift), _stream()), "moe_act_pairs")
     y = torch._grouped_mm(act, w_down.view(W, E, ff).permute(1, 2, 0), offs=offs)
     out = torch.empty((T, W), dtype=torch.float32, device=dev)
-    _check(rows_fn(2, _ptr(y), _dt(y), _ptr(pos), None, _ptr(out), T, W, top, 0.0, 0.0, _stream()), "moe_combine")
+    _check(rows_fn(2, _ptr(y), _dt(y), _ptr(pos), None, _ptr(out), T, W, top, 0.0, 0.0, 0.0, _stream()), "moe_combine")
     return out
 
 

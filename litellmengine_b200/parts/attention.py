@@ -244,8 +244,8 @@ class GatedAttentionMixer(BranchMixer):
         self.dv = spec.value_dim or spec.head_dim
         if not 0 < spec.head_dim <= 256 or not 0 < self.dv <= 256:
             raise ValueError("key and value widths must be between 1 and 256")
-        if spec.position.kind != "none":
-            raise ValueError("the gated attention mixer applies no position encoding of its own")
+        if spec.position.kind not in ("none", "rope_pairs"):
+            raise ValueError("the gated attention mixer rotates neighbouring pairs ('rope_pairs') or not at all")
         if spec.qk_norm_scope not in ("head", "projection"):
             raise ValueError(f"qk_norm_scope {spec.qk_norm_scope!r}: 'head' or 'projection'")
         if spec.output_gate not in (None, "sigmoid"):
@@ -260,6 +260,14 @@ class GatedAttentionMixer(BranchMixer):
         self.nq, self.nkv, self.d = spec.num_heads, spec.num_kv_heads, spec.head_dim
         self.scale = spec.scale if spec.scale is not None else 1.0 / math.sqrt(float(self.d))
         self.names = dict(self._DEFAULT_NAMES, **dict(spec.tensor_names))
+        # a rotation after the norm, inside the kernel that prepares q, k and v
+        self.rotation = None
+        if spec.position.kind != "none":
+            self.rotation = lookup("position", spec.position.kind)(spec.position, self.d, device).kernel_args()
+        self.keep_first = int(getattr(spec, "keep_first", 0)) if spec.window is not None else 0
+        self.sink = getattr(spec, "softmax_sink", None)
+        if self.keep_first < 0:
+            raise ValueError("keep_first must not be negative")
         self.q_off, self.k_off = 0, self.nq * self.d
         self.v_off = self.k_off + self.nkv * self.d
         self.g_off = self.v_off + self.nkv * self.dv
@@ -277,15 +285,17 @@ class GatedAttentionMixer(BranchMixer):
         # the tuned bfloat16 kernels read keys and values of one width from one tensor, add no bias to the
         # scores and leave the gate to a kernel that takes one value per channel
         self.head_temp = self.log_r1 = self.log_r2 = None     # float32 [heads] each, when the spec asks for them
-        scored = spec.head_temperature or spec.log_distance_bias      # the scores carry more than the tuned kernels know
+        # the scores or the key walk carry more than the tuned kernels know
+        scored = spec.head_temperature or spec.log_distance_bias
+        walked = self.keep_first > 0 or self.sink is not None          # kept first keys, a sink: the general kernel
         self._tuned = (compute_dtype == torch.bfloat16 and self.dv == self.d and self.device.type == "cuda"
-                       and spec.distance_bias is None and not self.gate_per_head and not scored
+                       and spec.distance_bias is None and not self.gate_per_head and not scored and not walked
                        and ops.fast_attention_supported(self.d, self.nq // self.nkv))
         # with a bias by distance or a gate per head: prompt portions still take a tensor-core kernel (the
         # mma.sync one, which adds the bias to its scores and gates as it stores), single tokens the general one
         if scored and spec.distance_bias is not None:
             raise ValueError("a distance table and a logarithmic distance bias or head temperature exclude one another")
-        self._tuned_prompt = (not self._tuned and compute_dtype == torch.bfloat16 and self.dv == self.d
+        self._tuned_prompt = (not self._tuned and not walked and compute_dtype == torch.bfloat16 and self.dv == self.d
                               and self.device.type == "cuda" and (self.gate_per_head or not spec.output_gate)
                               and ops.prefill_attention_supported(self.d))
         self._tuned_decode = self._tuned_prompt and ops.fast_attention_supported(self.d, self.nq // self.nkv)
@@ -352,7 +362,7 @@ class GatedAttentionMixer(BranchMixer):
         ops.prepare_streaming(self.w_o)
 
     def cache_need(self):
-        return PagedNeed(self.nkv, self.d, self.spec.window, None if self.dv == self.d else self.dv)
+        return PagedNeed(self.nkv, self.d, self.spec.window, None if self.dv == self.d else self.dv, self.keep_first)
 
     def step_prelude(self):
         return AttentionWork() if self._tuned or self._tuned_prompt else None
@@ -383,7 +393,8 @@ class GatedAttentionMixer(BranchMixer):
             proj, col0 + self.q_off, col0 + self.k_off, col0 + self.v_off, self.biases, self.q_norm_w, self.k_norm_w,
             s.qk_norm_scope if s.qk_norm is not None else None, s.qk_norm.eps if s.qk_norm is not None else 0.0,
             s.query_temperature, ctx.cache_keys, ctx.cache_values, b.positions, b.token_entry, b.entry_slot,
-            ctx.block_table, self.nq, self.nkv, self.d, self.dv, ctx.page_size, ctx.status, self.dtype)
+            ctx.block_table, self.nq, self.nkv, self.d, self.dv, ctx.page_size, ctx.status, self.dtype,
+            rotation=self.rotation)
         if self._tuned and ctx.cache is not None and b.preludes.get(AttentionWork.name) is not None:
             a = attention_over_pages(q, ctx, self.nq, self.nkv, self.d, s.window, self.scale)
             ops.gate_mul(a, proj, col0 + self.g_off, out, out_col0, s.output_gate, out_scale)
@@ -434,7 +445,8 @@ class GatedAttentionMixer(BranchMixer):
             self.nkv, self.d, self.dv, ctx.page_size, s.window, self.scale, ctx.status, out, out_col0,
             gate=proj if s.output_gate else None, gate_off=col0 + self.g_off, out_scale=out_scale,
             dist_bias=self.dist_table, gate_per_head=self.gate_per_head, rows=rows, head_scale=self.head_temp,
-            log_bias=(self.log_r1, self.log_r2) if self.log_r1 is not None else None)
+            log_bias=(self.log_r1, self.log_r2) if self.log_r1 is not None else None, keep_first=self.keep_first,
+            sink=self.sink)
 
 
 def distance_bucket(n: int, rows: int, far: float) -> int:

@@ -97,6 +97,12 @@ class Block:
                 spec.feed_forward, hidden_size, compute_dtype, device)
         else:
             self.feed_forward_norm = None
+        # norms on the sublayers' outputs, for arrangements that have them beside the ones in front
+        self.mixer_post_norm = self.feed_forward_post_norm = None
+        if getattr(spec, "mixer_post_norm", None) is not None:
+            self.mixer_post_norm = lookup("norm", spec.mixer_post_norm.kind)(spec.mixer_post_norm, hidden_size)
+        if getattr(spec, "feed_forward_post_norm", None) is not None and spec.feed_forward is not None:
+            self.feed_forward_post_norm = lookup("norm", spec.feed_forward_post_norm.kind)(spec.feed_forward_post_norm, hidden_size)
         self.arrangement = lookup("arrangement", spec.arrangement)
         # a model with several residual streams: one connection per sublayer
         self.connections = None
@@ -127,6 +133,10 @@ class Block:
         out = [(s.mixer_norm_name, self.mixer_norm), (s.mixer.weight_prefix, self.mixer)]
         if self.feed_forward is not None:
             out += [(s.feed_forward_norm_name, self.feed_forward_norm), (s.feed_forward.weight_prefix, self.feed_forward)]
+        if self.mixer_post_norm is not None:
+            out.append((s.mixer_post_norm_name, self.mixer_post_norm))
+        if self.feed_forward_post_norm is not None:
+            out.append((s.feed_forward_post_norm_name, self.feed_forward_post_norm))
         if self.connections is not None:
             out += [(name, c) for name, c in zip(s.connections[1:], self.connections) if c is not None]
         if self.input_convs is not None:
@@ -219,6 +229,24 @@ def branch_norm(block: Block, h: torch.Tensor, delta: Optional[torch.Tensor], ct
     if narrow is not None:
         tables["stream_copy"] = (h, x)
     return h, None
+
+
+@register_arrangement("sandwich_norm")
+def sandwich_norm(block: Block, h: torch.Tensor, delta, ctx: StageContext):
+    """h += norm1b(mixer(norm1(h))); h += norm2b(ffn(norm2(h))): a norm in front of every sublayer and one on its
+    output.  `h` is the float32 residual stream; a sublayer's output does not join it when the sublayer returns: it
+    travels on (across layers too) as a `PendingNormed` with the norm of its way, and the kernel that makes the next
+    sublayer's normed input adds it as it reads.  The norms must take a `PendingNormed` as their `delta`."""
+    from .norms import PendingNormed
+    x = block.mixer_norm.forward(h, block.dtype, delta=delta, write_sum=delta is not None)
+    ctx.partials_ok = True                                      # the norm kernel adds a product's k-splits as it reads
+    ctx.residual = None                                         # a norm stands between the product and the stream
+    pending = PendingNormed(block.mixer.forward(x, ctx), block.mixer_post_norm)
+    if block.feed_forward is not None:
+        x = block.feed_forward_norm.forward(h, block.dtype, delta=pending, write_sum=True)
+        extra = {"partials_ok": True} if getattr(block.feed_forward, "supports_partials", False) else {}
+        pending = PendingNormed(block.feed_forward.forward(x, **extra), block.feed_forward_post_norm)
+    return h, pending
 
 
 @register_arrangement("post_norm")

@@ -72,7 +72,14 @@ class RoutedExperts:
     chosen experts' matrices.  Otherwise (decode steps that touch most experts anyway; the 32-bit mode): one
     product gives every expert's gate and up values, the activation kernel multiplies each expert's activations
     by the token's weight for it (zero for experts that were not chosen) and ONE down product adds the chosen
-    experts' outputs up."""
+    experts' outputs up.
+
+    Options of the spec's `params`: `score` 'sigmoid' (above) or 'softmax' (over all router outputs); `correction`:
+    a stored vector (tensor 'correction') is added to the scores for the CHOICE only, the weights are made of the
+    scores themselves; `identity` = n: the router has n more outputs than experts, and a token that picks one of
+    them gets its own input back times the weight; `activation` 'silu': an expert is down(silu(gate x) * (up x))
+    without clamps; `shared` = ff: one more gated feed-forward of that size (tensors 'shared.gate', 'shared.up',
+    'shared.down', the routed experts' activation) runs for every token and is added."""
 
     graph_safe = True
     any_division_safe = True
@@ -85,10 +92,32 @@ class RoutedExperts:
         self.hidden, self.ff, self.dtype = hidden_size, spec.intermediate_size, compute_dtype
         self.E, self.top = int(p["experts"]), int(p["top"])
         self.groups = tuple(p["groups"]) if p.get("groups") else None
-        self.route_scale, self.limit = float(p.get("route_scale", 1.0)), float(p["limit"])
+        self.route_scale = float(p.get("route_scale", 1.0))
+        # the experts' activation as (clamp, slope inside the sigmoid, what is added to the up value)
+        self.activation = p.get("activation", "clamped_swish")
+        if self.activation == "clamped_swish":
+            self.limit, self.act_alpha, self.act_shift = float(p["limit"]), self.ACT_ALPHA, 1.0
+        elif self.activation == "silu":
+            self.limit, self.act_alpha, self.act_shift = float("inf"), 1.0, 0.0
+        else:
+            raise ValueError(f"activation {self.activation!r}: 'clamped_swish' or 'silu'")
+        self.score = p.get("score", "sigmoid")
+        self.identity = int(p.get("identity", 0) or 0)
+        self.has_correction = bool(p.get("correction", False))
+        self.correction = None
+        self.shared = None
+        if p.get("shared"):
+            self.shared = SwiGLU(FeedForwardSpec(kind="swiglu", intermediate_size=int(p["shared"]),
+                                                 params=(("activation", "silu"),),
+                                                 tensor_names=(("gate", "gate"), ("up", "up"), ("down", "down"))),
+                                 hidden_size, compute_dtype, device)
         self.prefix = p.get("expert_prefix", "e")
-        if self.ff <= 0 or self.E <= 0 or not 0 < self.top <= self.E:
-            raise ValueError("routed experts need a positive size, experts and 0 < top <= experts")
+        if self.ff <= 0 or self.E <= 0 or self.identity < 0 or not 0 < self.top <= self.E + self.identity:
+            raise ValueError("routed experts need a positive size, experts and 0 < top <= the router's outputs")
+        if self.score not in ("sigmoid", "softmax"):
+            raise ValueError(f"score {self.score!r}: 'sigmoid' or 'softmax'")
+        if self.groups is not None and self.identity:
+            raise ValueError("expert groups and router outputs without an expert exclude one another")
         if self.groups is not None:
             count, keep = self.groups
             if self.E % count or not 0 < keep <= count or keep * (self.E // count) < self.top:
@@ -96,7 +125,11 @@ class RoutedExperts:
         self.w_router = self.w_gate_up = self.w_down = None
 
     def parameters(self) -> Dict[str, ParamSpec]:
-        out = {"router": ParamSpec((self.E, self.hidden), role="scale", init=("normal", 0.5))}
+        out = {"router": ParamSpec((self.E + self.identity, self.hidden), role="scale", init=("normal", 0.5))}
+        if self.has_correction:
+            out["correction"] = ParamSpec((self.E + self.identity,), role="scale", init=("normal", 0.05))
+        if self.shared is not None:
+            out.update({f"shared.{n}": ps for n, ps in self.shared.parameters().items()})
         for e in range(self.E):
             out[f"{self.prefix}{e}.gate"] = ParamSpec((self.ff, self.hidden))
             out[f"{self.prefix}{e}.up"] = ParamSpec((self.ff, self.hidden))
@@ -105,6 +138,10 @@ class RoutedExperts:
 
     def load(self, t: Dict[str, torch.Tensor]) -> None:
         self.w_router = t["router"].float().contiguous()
+        if self.has_correction:
+            self.correction = t["correction"].float().contiguous()
+        if self.shared is not None:
+            self.shared.load({n: t[f"shared.{n}"] for n in self.shared.parameters()})
         rows = [t[f"{self.prefix}{e}.{k}"] for e in range(self.E) for k in ("gate", "up")]
         downs = [t[f"{self.prefix}{e}.down"] for e in range(self.E)]
         dt = torch.float32 if any(x.dtype == torch.float32 for x in rows + downs) else rows[0].dtype
@@ -113,17 +150,35 @@ class RoutedExperts:
         ops.prepare_streaming(self.w_gate_up)
         ops.prepare_streaming(self.w_down)
 
+    def _route(self, x: torch.Tensor, lists: bool):
+        """(dense weights or None, ids, weights, the tokens' share of their own input or None)."""
+        got = ops.moe_route(x, self.w_router, self.top, self.groups, self.route_scale, lists=lists, score=self.score,
+                            correction=self.correction, identity=self.identity)
+        if lists:
+            return got if self.identity else got + (None,)
+        return (got[0], None, None, got[1]) if self.identity else (got, None, None, None)
+
     def forward(self, x: torch.Tensor, partials_ok: bool = False):
         T = x.shape[0]
+        act = (self.limit, self.act_alpha)
+        plain = self.identity == 0 and self.shared is None        # nothing joins the experts' sum
         if (T * self.top < self.E and x.dtype == self.w_gate_up.dtype == self.w_down.dtype and self.hidden <= 12288
                 and self.top * self.ff <= 12288):
-            _, ids, weights = ops.moe_route(x, self.w_router, self.top, self.groups, self.route_scale, lists=True)
-            return ops.moe_sparse(x, self.w_gate_up, self.w_down, ids, weights, self.ff, self.limit, self.ACT_ALPHA)
-        if (T > self.SORTED_FROM and x.dtype == torch.bfloat16 and self.w_gate_up.dtype == self.w_down.dtype == torch.bfloat16
+            _, ids, weights, own = self._route(x, True)
+            out = ops.moe_sparse(x, self.w_gate_up, self.w_down, ids, weights, self.ff, *act, shift=self.act_shift)
+        elif (T > self.SORTED_FROM and x.dtype == torch.bfloat16 and self.w_gate_up.dtype == self.w_down.dtype == torch.bfloat16
                 and self.hidden % 8 == 0 and self.ff % 8 == 0 and self.E <= 4096 and ops.grouped_product_available()):
-            _, ids, weights = ops.moe_route(x, self.w_router, self.top, self.groups, self.route_scale, lists=True)
-            return ops.moe_sorted(x, self.w_gate_up, self.w_down, ids, weights, self.E, self.ff, self.limit, self.ACT_ALPHA)
-        dense = ops.moe_route(x, self.w_router, self.top, self.groups, self.route_scale)
-        gate_up = ops.linear(x, self.w_gate_up, out_dtype=torch.float32, partials_ok=True)
-        act = ops.moe_act(gate_up, dense, self.E, self.ff, self.limit, self.ACT_ALPHA, self.dtype)
-        return ops.linear(act, self.w_down, out_dtype=torch.float32, partials_ok=partials_ok)
+            _, ids, weights, own = self._route(x, True)
+            out = ops.moe_sorted(x, self.w_gate_up, self.w_down, ids, weights, self.E, self.ff, *act, shift=self.act_shift)
+        else:
+            dense, _, _, own = self._route(x, False)
+            gate_up = ops.linear(x, self.w_gate_up, out_dtype=torch.float32, partials_ok=True)
+            a = ops.moe_act(gate_up, dense, self.E, self.ff, *act, self.dtype, shift=self.act_shift)
+            out = ops.linear(a, self.w_down, out_dtype=torch.float32, partials_ok=partials_ok and plain)
+        if plain:
+            return out
+        # the token's own input times what it gave to outputs without an expert, and the shared expert, join in 32-bit
+        shared = self.shared.forward(x, partials_ok=True) if self.shared is not None else None
+        if isinstance(shared, ops.PartialSum) and shared.rounds_to is not None:
+            shared = ops.as_tensor(shared)
+        return ops.moe_finish(ops.as_tensor(out), x, own, shared)

@@ -23,7 +23,7 @@ class LatentAttentionMixer:
         [d | kr] = W_dkv x                      c = rmsnorm(d) * w_dkv (R),  kr (P) rotated by position, shared by all heads
         key[h] = [W_uk[h] c | kr]               value[h] = W_uv[h] c
         score(i, j) = (qn_i[h] . W_uk[h] c_j + qr_i[h] . kr_j) * scale        over the keys of the window, softmax
-        out = W_o (concat_h(sum_j p_j value_j[h]) * sigmoid(W_g x))
+        out = W_o (concat_h(sum_j p_j value_j[h]) * sigmoid(W_g x))      (the gate one value per channel, or per head)
 
     Only the row [c | kr] (R + P entries, ONE "kv head") goes to the pages.  The per-head maps are folded into the
     query and the output, q_abs[h] = W_uk[h]^T qn[h] and sum_j p_j value_j[h] = W_uv[h] sum_j p_j c_j, so attention
@@ -61,16 +61,22 @@ class LatentAttentionMixer:
         self.spec, self.hidden, self.dtype, self.device = spec, hidden_size, compute_dtype, torch.device(device)
         self.scale = spec.scale if spec.scale is not None else 1.0 / math.sqrt(float(self.D + self.P))
         self.names = dict(self._DEFAULT_NAMES, **dict(spec.tensor_names))
-        self.rot_dims, self.inv_freq = 0, None
+        self.rot_dims, self.inv_freq, self.rot_pairs, self.rot_mag = 0, None, False, 1.0
         if spec.position.kind == "rope" and self.P:
             pos = lookup("position", "rope")(spec.position, self.P, device)       # the rotation's frequencies, float32
             self.rot_dims, self.inv_freq = pos.rotary_dim, pos.inv_freq
+        elif spec.position.kind == "rope_pairs" and self.P:                       # neighbouring pairs, stretched frequencies
+            self.inv_freq, self.rot_dims, self.rot_mag, self.rot_pairs = lookup("position", "rope_pairs")(
+                spec.position, self.P, device).kernel_args()
         elif spec.position.kind != "none":
-            raise ValueError("latent attention rotates by 'rope' or not at all")
+            raise ValueError("latent attention rotates by 'rope', by 'rope_pairs' or not at all")
+        if spec.output_gate_scope not in ("channel", "head"):
+            raise ValueError(f"output_gate_scope {spec.output_gate_scope!r}: 'channel' or 'head'")
+        self.gate_per_head = bool(spec.output_gate) and spec.output_gate_scope == "head"
         self.dq_off = 0
         self.dkv_off = self.Q
         self.g_off = self.Q + (self.R + self.P if spec.has_kv else 0)
-        self.gate_width = self.H * self.V if spec.output_gate else 0
+        self.gate_width = 0 if not spec.output_gate else (self.H if self.gate_per_head else self.H * self.V)
         # bfloat16 on the tensor-core kernel over the cached rows; float32 (and other latent sizes) on the general kernel
         self.tensor_core = (compute_dtype == torch.bfloat16 and self.device.type == "cuda"
                             and ops.latent_attention_supported(self.R, self.P))
@@ -119,9 +125,10 @@ class LatentAttentionMixer:
         proj = ops.as_tensor(ops.linear(x, self.w_in, out_dtype=torch.float32))
         cq = ops.latent_prepare(proj, self.dq_off, self.dkv_off, self.Q, R, P, self.rot_dims, self.wq_norm, self.wkv_norm,
                                 self.eps, self.inv_freq, ctx.cache_keys if s.has_kv else None, b, ctx.block_table,
-                                ctx.page_size, ctx.status, self.dtype)
+                                ctx.page_size, ctx.status, self.dtype, rot_pairs=self.rot_pairs, rot_mag=self.rot_mag)
         q = ops.as_tensor(ops.linear(cq, self.w_uq, out_dtype=torch.float32))
-        qn, packed = ops.latent_q_split(q, b.positions, self.inv_freq, H, D, P, R, self.rot_dims, self.dtype)
+        qn, packed = ops.latent_q_split(q, b.positions, self.inv_freq, H, D, P, R, self.rot_dims, self.dtype,
+                                        rot_pairs=self.rot_pairs, rot_mag=self.rot_mag)
         # q_abs[h] = qn[h] W_uk[h], written into the first R columns of head h of the packed query
         torch.bmm(qn, self.w_uk_t if self.w_uk_t.dtype == qn.dtype else self.w_uk_t.to(qn.dtype),
                   out=packed.view(T, H, R + P)[:, :, :R].permute(1, 0, 2))
@@ -137,5 +144,5 @@ class LatentAttentionMixer:
         torch.bmm(lat.view(T, H, R).permute(1, 0, 2), self.w_uv_t if self.w_uv_t.dtype == lat.dtype else self.w_uv_t.to(lat.dtype),
                   out=heads.view(T, H, V).permute(1, 0, 2))
         if s.output_gate:
-            ops.gate_mul(heads, proj, self.g_off, heads, 0, s.output_gate)
+            ops.gate_mul(heads, proj, self.g_off, heads, 0, s.output_gate, per_head=V if self.gate_per_head else 0)
         return ops.linear(heads, self.w_o, out_dtype=torch.float32, partials_ok=getattr(ctx, "partials_ok", False))

@@ -53,10 +53,15 @@ class Model:
         for spec, block in zip(p.blocks, self.blocks):
             for name, ps in block.parameters().items():
                 out[f"{spec.weight_prefix}.{name}"] = ps
-        out[p.final_norm_name] = next(iter(self.final_norm.parameters().values()))
+        for k, (name, ps) in enumerate(self.final_norm.parameters().items()):
+            out[self._final_norm_tensor(k, name)] = ps
         out[p.output_name] = ParamSpec((p.vocab_size, p.hidden_size),
                                        optional_alias=p.embedding_name if p.tie_word_embeddings else None)
         return out
+
+    def _final_norm_tensor(self, k: int, name: str) -> str:
+        """The final norm's first tensor is `final_norm_name` itself; further ones (a bias, a scalar) stand beside it."""
+        return self.plan.final_norm_name if k == 0 else f"{self.plan.final_norm_name}.{name}"
 
     def load_weights(self, source: WeightSource, where: str = "") -> None:
         """Check the whole source first (one error for everything wrong), then bind part by
@@ -74,7 +79,8 @@ class Model:
             # a tensor that may be absent and is: the part is handed nothing for it
             block.load({n: get(f"{spec.weight_prefix}.{n}") for n, ps in block.parameters().items()
                         if not (ps.optional and f"{spec.weight_prefix}.{n}" not in have)})
-        self.final_norm.load({next(iter(self.final_norm.parameters())): get(p.final_norm_name)})
+        self.final_norm.load({name: get(self._final_norm_tensor(k, name))
+                              for k, name in enumerate(self.final_norm.parameters())})
         self.output = self.embedding if p.output_name in aliased else get(p.output_name).contiguous()
         ops.prepare_streaming(self.output)          # a tiled copy of the output head for decode steps
 

@@ -104,3 +104,41 @@ class RotaryPosition:
         if self._key not in tables:
             tables[self._key] = ops.rope_angles(batch.positions, self.inv_freq)
         return tables[self._key]
+
+
+@register_position("rope_pairs")
+class PairRotation:
+    """Rotation of neighbouring pairs: entries 2i and 2i + 1 of the first `rotary_dim` entries of a head turn by the
+    angle float(position) * freq[i]; (a, b) becomes (a cos - b sin, b cos + a sin) * magnitude.  freq[i] =
+    theta^(-2i/rotary_dim), stretched by `scaling` = (factor, original, fast, slow) where the spec has one: pairs
+    whose wavelength is long against the original context are slowed by `factor`, short ones stay, with a linear
+    ramp over the pair index between the two (see `PositionSpec`).  The table is made once, in double precision, and
+    rounded to float32; angle, sine and cosine are 32-bit inside the kernels that rotate.  A mixer reads `freq`,
+    `rotary_dim`, `magnitude` and `pairs` and hands them to its kernel."""
+
+    pairs = True
+
+    def __init__(self, spec: PositionSpec, head_dim: int, device):
+        import math
+        rd = spec.rotary_dim or head_dim
+        if rd <= 0 or rd % 2 or rd > head_dim:
+            raise ValueError(f"rotary_dim {rd} must be even and at most {head_dim}")
+        if not spec.theta > 1.0:
+            raise ValueError("the rotation's base must exceed 1")
+        p = dict(spec.params)
+        base = float(spec.theta)
+        freq = [base ** (-2.0 * i / rd) for i in range(rd // 2)]
+        if p.get("scaling") is not None:
+            factor, original, fast, slow = (float(v) for v in p["scaling"])
+            pair = lambda turns: rd * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(base))
+            lo, hi = max(math.floor(pair(fast)), 0), min(math.ceil(pair(slow)), rd - 1)
+            for i in range(rd // 2):
+                ramp = min(max((i - lo) / max(hi - lo, 0.001), 0.0), 1.0)
+                freq[i] = freq[i] / factor * ramp + freq[i] * (1.0 - ramp)
+        self.rotary_dim = rd
+        self.magnitude = float(p.get("magnitude", 1.0))
+        self.freq = torch.tensor(freq, dtype=torch.float64).to(torch.float32).to(device).contiguous()
+
+    def kernel_args(self):
+        """(freq, dims, magnitude, pairs) as the rotating kernels take them."""
+        return (self.freq, self.rotary_dim, self.magnitude, self.pairs)
