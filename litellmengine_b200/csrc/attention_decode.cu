@@ -65,7 +65,7 @@ __global__ void __launch_bounds__(AD_THREADS) paged_decode_attention_kernel(
     const int32_t* __restrict__ entry_slot, const int32_t* __restrict__ block_table, int table_stride,
     float* __restrict__ part_acc, float* __restrict__ part_ml, bf16* __restrict__ out, int nq, int nkv,
     int page_size, int window, float scale_log2e, int num_pages, int num_splits, int32_t* __restrict__ status,
-    const float* __restrict__ dist_bias, int dist_len) {
+    const float* __restrict__ dist_bias, int dist_len, int keep_first, int has_sink, float sink_log2) {
     pdl_begin();
     constexpr int CH = D / 8, KB = D / 16;
     extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -91,10 +91,15 @@ __global__ void __launch_bounds__(AD_THREADS) paged_decode_attention_kernel(
     const int32_t* table = block_table + static_cast<size_t>(entry_slot[token_entry[t]]) * table_stride;
     const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
     const int n_keys = pos - lo + 1;
-    int per_split = (n_keys + num_splits - 1) / num_splits;
+    // BIAS, with a window and kept first keys: the LAST split walks the kept keys below the window, [0, min(keep_first,
+    // lo)), and the others share the window; the merge kernel adds it like any other split.
+    const bool kept = BIAS && keep_first > 0 && window > 0;
+    const int window_splits = kept ? num_splits - 1 : num_splits;
+    int per_split = (n_keys + window_splits - 1) / window_splits;
     per_split = (per_split + AD_BN - 1) / AD_BN * AD_BN;
-    const int k_begin = lo + split * per_split;
-    const int k_end = min(pos + 1, k_begin + per_split);
+    const bool head_split = kept && split == window_splits;
+    const int k_begin = head_split ? 0 : lo + split * per_split;
+    const int k_end = head_split ? min(keep_first, lo) : min(pos + 1, k_begin + per_split);
     const int n_tiles = k_end > k_begin ? (k_end - k_begin + AD_BN - 1) / AD_BN : 0;
 
     const size_t head_stride = static_cast<size_t>(page_size) * D;
@@ -266,7 +271,7 @@ __global__ void __launch_bounds__(AD_THREADS) paged_decode_attention_kernel(
     __syncthreads();
     for (int i = tid; i < G * D; i += AD_THREADS) {
         const int g = i / D, dim = i - g * D;
-        float M = fmaxf(fmaxf(m_s[0][g], m_s[1][g]), fmaxf(m_s[2][g], m_s[3][g]));
+        const float M = fmaxf(fmaxf(m_s[0][g], m_s[1][g]), fmaxf(m_s[2][g], m_s[3][g]));
         float a = 0.0f, L = 0.0f;
 #pragma unroll
         for (int w = 0; w < 4; ++w) {
@@ -275,6 +280,7 @@ __global__ void __launch_bounds__(AD_THREADS) paged_decode_attention_kernel(
             L += l_s[w][g] * f;
         }
         if (num_splits == 1) {
+            if (BIAS && has_sink) L += exp2f(sink_log2 - M);        // one more term in the denominator, without a value
             out[(static_cast<size_t>(t) * nq + h0 + g) * D + dim] = __float2bfloat16_rn(a / L);
         } else {
             const size_t hrow = static_cast<size_t>(r) * nq + h0 + g;
@@ -293,7 +299,7 @@ __global__ void __launch_bounds__(AD_THREADS) paged_decode_attention_kernel(
 template <int D>
 __global__ void paged_decode_combine_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
                                             const int32_t* __restrict__ rows, bf16* __restrict__ out, int nq,
-                                            int num_splits) {
+                                            int num_splits, int has_sink, float sink_log2) {
     pdl_begin();
     const int r = blockIdx.x, h = blockIdx.y;
     const int t = rows ? rows[r] : r;
@@ -312,6 +318,7 @@ __global__ void paged_decode_combine_kernel(const float* __restrict__ part_acc, 
                 L += ls * f;
             }
         }
+        if (has_sink && M != -CUDART_INF_F) L += exp2f(sink_log2 - M);      // a term of the denominator without a value
         out[(static_cast<size_t>(t) * nq + h) * D + dim] = __float2bfloat16_rn(a / L);
     }
 }
@@ -321,9 +328,11 @@ static int launch_decode(const bf16* q, const bf16* cache, const int32_t* rows, 
                          const int32_t* token_entry, const int32_t* entry_slot, const int32_t* block_table,
                          int table_stride, float* part_acc, float* part_ml, bf16* out, int n_rows, int nq, int nkv,
                          int page_size, int window, float scale, int num_pages, int num_splits, int32_t* status,
-                         const float* dist_bias, int dist_len, cudaStream_t s) {
+                         const float* dist_bias, int dist_len, int keep_first, int has_sink, float sink_score, cudaStream_t s) {
     const size_t smem = static_cast<size_t>(16 + 2 * AD_STAGES * AD_BN) * D * sizeof(bf16);
-    auto kern = dist_bias ? paged_decode_attention_kernel<D, AD_STAGES, true> : paged_decode_attention_kernel<D, AD_STAGES, false>;
+    const bool ext = dist_bias || (keep_first > 0 && window > 0) || has_sink;      // the instantiation that knows them
+    const float sink_log2 = sink_score * 1.4426950408889634f;
+    auto kern = ext ? paged_decode_attention_kernel<D, AD_STAGES, true> : paged_decode_attention_kernel<D, AD_STAGES, false>;
     if (smem > 48 * 1024) {
         const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
         if (e != cudaSuccess) return static_cast<int>(e);
@@ -335,26 +344,28 @@ static int launch_decode(const bf16* q, const bf16* cache, const int32_t* rows, 
 #define TMA_GO(TS)                                                                                                   \
     {                                                                                                                \
         const size_t tsmem = static_cast<size_t>(2 * TS * AD_BN + 16) * D * sizeof(bf16) + 1024;                     \
-        auto tk = dist_bias ? paged_decode_attention_tma_kernel<D, TS, true> : paged_decode_attention_tma_kernel<D, TS, false>; \
+        auto tk = ext ? paged_decode_attention_tma_kernel<D, TS, true> : paged_decode_attention_tma_kernel<D, TS, false>; \
         const cudaError_t te = cudaFuncSetAttribute(tk, cudaFuncAttributeMaxDynamicSharedMemorySize,                 \
                                                     static_cast<int>(tsmem));                                        \
         if (te != cudaSuccess) return static_cast<int>(te);                                                          \
         launch_pdl(tk, dim3(grid), dim3(AD_THREADS + 32), tsmem, s, *map, q, rows, positions, token_entry, entry_slot, block_table,      \
                                                 table_stride, part_acc, part_ml, out, nq, nkv, page_size, window,    \
                                                 scale * 1.4426950408889634f, num_pages, num_splits, status,          \
-                                                dist_bias, dist_len);                                                \
+                                                dist_bias, dist_len, keep_first, has_sink, sink_log2);               \
     }
         TMA_GO(3)                                                   // three tiles in shared memory: one read, two in flight
 #undef TMA_GO
     } else {
         launch_pdl(kern, dim3(grid), dim3(AD_THREADS), smem, s, q, cache, rows, positions, token_entry, entry_slot, block_table, table_stride,
                                             part_acc, part_ml, out, nq, nkv, page_size, window,
-                                            scale * 1.4426950408889634f, num_pages, num_splits, status, dist_bias, dist_len);
+                                            scale * 1.4426950408889634f, num_pages, num_splits, status, dist_bias, dist_len,
+                                            keep_first, has_sink, sink_log2);
     }
     int rc = launch_status();
     if (rc != LLM_OK || num_splits == 1) return rc;
     dim3 cgrid(n_rows, nq);
-    launch_pdl((paged_decode_combine_kernel<D>), cgrid, dim3(D <= 64 ? 64 : 128), 0, s, part_acc, part_ml, rows, out, nq, num_splits);
+    launch_pdl((paged_decode_combine_kernel<D>), cgrid, dim3(D <= 64 ? 64 : 128), 0, s, part_acc, part_ml, rows, out, nq, num_splits,
+               has_sink, sink_log2);
     return launch_status();
 }
 
@@ -375,12 +386,16 @@ extern "C" long long llm_paged_decode_scratch_floats(int n_rows, int nq, int d, 
 // log2 e); row min(p - j, dist_len - 1) of a head joins the scaled score of the query at p and key j.  dist_len == -1:
 // `dist_bias` is float32 [nq, 3], per head a temperature on the scaled score and the two numbers of the bias
 // r1 * ln(1 + r2 * (p - j)) that is taken off it.
-extern "C" int llm_paged_attention_decode_biased(
+// `keep_first` (with a window): the sequence's first so many keys stay visible; `num_splits` then counts one split
+// more than the window's, which walks them.  `has_sink`: one more term exp(sink_score) in the softmax's denominator.
+extern "C" int llm_paged_attention_decode_ex(
     const void* q, void* out, const void* cache, const int32_t* rows, int n_rows, const int32_t* positions,
     const int32_t* token_entry, const int32_t* entry_slot, const int32_t* block_table, int table_stride, int nq,
     int nkv, int d, int page_size, int window, float scale, int num_pages, int num_splits, float* scratch,
-    int32_t* status, const float* dist_bias, int dist_len, uintptr_t stream) {
+    int32_t* status, const float* dist_bias, int dist_len, int keep_first, int has_sink, float sink_score,
+    uintptr_t stream) {
     if (n_rows <= 0) return LLM_OK;
+    if (keep_first < 0 || (keep_first > 0 && window > 0 && num_splits < 2)) return LLM_REFUSED_SIZE;
     if (dist_bias && dist_len <= 0 && dist_len != -1) return LLM_REFUSED_SIZE;
     if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || page_size <= 0 || num_splits < 1 || num_splits > 65535 ||
         nkv > 65535 || n_rows > 65535)
@@ -396,10 +411,20 @@ extern "C" int llm_paged_attention_decode_biased(
     return launch_decode<DD, SS>(static_cast<const bf16*>(q), static_cast<const bf16*>(cache), rows, positions, \
                                  token_entry, entry_slot, block_table, table_stride, part_acc, part_ml,         \
                                  static_cast<bf16*>(out), n_rows, nq, nkv, page_size, window, scale, num_pages, \
-                                 num_splits, status, dist_bias, dist_len, s)
+                                 num_splits, status, dist_bias, dist_len, keep_first, has_sink, sink_score, s)
     if (d == 64) GO(64, 3);
     GO(128, 3);
 #undef GO
+}
+
+extern "C" int llm_paged_attention_decode_biased(
+    const void* q, void* out, const void* cache, const int32_t* rows, int n_rows, const int32_t* positions,
+    const int32_t* token_entry, const int32_t* entry_slot, const int32_t* block_table, int table_stride, int nq,
+    int nkv, int d, int page_size, int window, float scale, int num_pages, int num_splits, float* scratch,
+    int32_t* status, const float* dist_bias, int dist_len, uintptr_t stream) {
+    return llm_paged_attention_decode_ex(q, out, cache, rows, n_rows, positions, token_entry, entry_slot, block_table,
+                                         table_stride, nq, nkv, d, page_size, window, scale, num_pages, num_splits, scratch,
+                                         status, dist_bias, dist_len, 0, 0, 0.0f, stream);
 }
 
 extern "C" int llm_paged_attention_decode(

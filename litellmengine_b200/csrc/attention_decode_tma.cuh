@@ -71,7 +71,7 @@ __global__ void __launch_bounds__(AD_THREADS + 32) paged_decode_attention_tma_ke
     const int32_t* __restrict__ entry_slot, const int32_t* __restrict__ block_table, int table_stride,
     float* __restrict__ part_acc, float* __restrict__ part_ml, bf16* __restrict__ out, int nq, int nkv,
     int page_size, int window, float scale_log2e, int num_pages, int num_splits, int32_t* __restrict__ status,
-    const float* __restrict__ dist_bias, int dist_len) {
+    const float* __restrict__ dist_bias, int dist_len, int keep_first, int has_sink, float sink_log2) {
     // The wait for the kernel before this one (which writes q and this step's key and value row)
     // comes late: keys and values of earlier steps, the block table and the step's metadata are
     // read first, so the first tiles are already on their way when q arrives.
@@ -105,10 +105,15 @@ __global__ void __launch_bounds__(AD_THREADS + 32) paged_decode_attention_tma_ke
     const int32_t* table = block_table + static_cast<size_t>(entry_slot[token_entry[t]]) * table_stride;
     const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
     const int n_keys = pos - lo + 1;
-    int per_split = (n_keys + num_splits - 1) / num_splits;
+    // BIAS, with a window and kept first keys: the LAST split walks the kept keys below the window, [0, min(keep_first,
+    // lo)), and the others share the window; the merge kernel adds it like any other split.
+    const bool kept = BIAS && keep_first > 0 && window > 0;
+    const int window_splits = kept ? num_splits - 1 : num_splits;
+    int per_split = (n_keys + window_splits - 1) / window_splits;
     per_split = (per_split + AD_BN - 1) / AD_BN * AD_BN;
-    const int k_begin = lo + split * per_split;
-    const int k_end = min(pos + 1, k_begin + per_split);
+    const bool head_split = kept && split == window_splits;
+    const int k_begin = head_split ? 0 : lo + split * per_split;
+    const int k_end = head_split ? min(keep_first, lo) : min(pos + 1, k_begin + per_split);
     const int k_origin = (k_begin / AD_BN) * AD_BN;                  // tiles are whole pages
     const int n_tiles = k_end > k_begin ? (k_end - k_origin + AD_BN - 1) / AD_BN : 0;
 
@@ -313,6 +318,7 @@ __global__ void __launch_bounds__(AD_THREADS + 32) paged_decode_attention_tma_ke
             L += l_s[w][g] * f;
         }
         if (num_splits == 1) {
+            if (BIAS && has_sink) L += exp2f(sink_log2 - M);        // one more term in the denominator, without a value
             out[(static_cast<size_t>(t) * nq + h0 + g) * D + dim] = __float2bfloat16_rn(a / L);
         } else {
             const size_t hrow = static_cast<size_t>(r) * nq + h0 + g;

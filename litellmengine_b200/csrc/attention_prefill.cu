@@ -66,7 +66,7 @@ __global__ void __launch_bounds__(AP_THREADS) paged_prefill_attention_kernel(
     const int32_t* __restrict__ block_table, int table_stride, int nq, int nkv, int page_size, int window,
     float scale_log2e, int num_pages, int32_t* __restrict__ status,
     const float* __restrict__ dist_bias, int dist_len, const float* __restrict__ head_gate, long long gate_stride,
-    int gate_off, float out_scale, long long out_stride, int out_off) {
+    int gate_off, float out_scale, long long out_stride, int out_off, int keep_first, int has_sink, float sink_log2) {
     pdl_begin();
     constexpr int CH = D / 8;                     // 16-byte chunks per row
     constexpr int KB = D / 16;                    // k-blocks of the first product
@@ -88,7 +88,12 @@ __global__ void __launch_bounds__(AP_THREADS) paged_prefill_attention_kernel(
 
     const int pos_first = past + q0, pos_last = past + q0 + rows_here - 1;
     const int k_lo = (window > 0 && pos_first - window + 1 > 0) ? ((pos_first - window + 1) / AP_BN) * AP_BN : 0;
-    const int n_tiles = (pos_last - k_lo) / AP_BN + 1;
+    // EXT, with a window: the sequence's first `keep_first` keys stay visible.  The tiles that hold them and lie wholly
+    // below the window's first tile are walked first; kept keys inside the window's tiles are a matter of the mask.
+    const int keep = (EXT && window > 0) ? keep_first : 0;
+    const int head_tiles = min((keep + AP_BN - 1) / AP_BN, k_lo / AP_BN);
+    const int n_tiles = head_tiles + (pos_last - k_lo) / AP_BN + 1;
+    auto tile_key = [&](int it) { return it < head_tiles ? it * AP_BN : k_lo + (it - head_tiles) * AP_BN; };
 
     const size_t head_stride = static_cast<size_t>(page_size) * D;
     const size_t page_stride = 2 * static_cast<size_t>(nkv) * head_stride;
@@ -134,7 +139,7 @@ __global__ void __launch_bounds__(AP_THREADS) paged_prefill_attention_kernel(
             cp_async16(tile_at<D>(q_s, qr, c), src + c * 8, valid);
         }
     }
-    load_kv(k_lo, 0);
+    load_kv(tile_key(0), 0);
     cp_async_commit();
 
     unsigned qf[KB][4];
@@ -161,10 +166,10 @@ __global__ void __launch_bounds__(AP_THREADS) paged_prefill_attention_kernel(
     }
 
     for (int it = 0; it < n_tiles; ++it) {
-        const int kt = k_lo + it * AP_BN, buf = it & 1;
+        const int kt = tile_key(it), buf = it & 1;
         cp_async_wait_all();
         __syncthreads();
-        if (it + 1 < n_tiles) load_kv(kt + AP_BN, buf ^ 1);
+        if (it + 1 < n_tiles) load_kv(tile_key(it + 1), buf ^ 1);
         cp_async_commit();
         if (it == 0) {
 #pragma unroll
@@ -224,8 +229,8 @@ __global__ void __launch_bounds__(AP_THREADS) paged_prefill_attention_kernel(
                     b2 -= br1 * __log2f(1.0f + br2 * static_cast<float>(max(pos1 - key, 0)));
                 }
                 if (need_mask) {
-                    if (key > pos0 || key < lo0) a = -CUDART_INF_F;
-                    if (key > pos1 || key < lo1) b2 = -CUDART_INF_F;
+                    if (key > pos0 || (key < lo0 && key >= keep)) a = -CUDART_INF_F;
+                    if (key > pos1 || (key < lo1 && key >= keep)) b2 = -CUDART_INF_F;
                 }
                 s[nb][c] = a;
                 s[nb][2 + c] = b2;
@@ -276,6 +281,10 @@ __global__ void __launch_bounds__(AP_THREADS) paged_prefill_attention_kernel(
     }
     cp_async_wait_all();
 
+    if (EXT && has_sink) {                            // one more term in the denominator, without a value
+        if (m0 != -CUDART_INF_F) l0 += exp2f(sink_log2 - m0);
+        if (m1 != -CUDART_INF_F) l1 += exp2f(sink_log2 - m1);
+    }
     float inv0 = live0 && l0 > 0.0f ? out_scale / l0 : 0.0f, inv1 = live1 && l1 > 0.0f ? out_scale / l1 : 0.0f;
     if (EXT && head_gate) {                           // one sigmoid gate per (token, head)
         if (live0) inv0 *= 1.0f / (1.0f + expf(-head_gate[static_cast<size_t>(row_base + r0) * gate_stride + gate_off + h]));
@@ -299,7 +308,8 @@ extern "C" int llm_paged_attention_prefill_ex(
     const int32_t* entry_q_start, const int32_t* entry_q_len, const int32_t* entry_kv_len,
     const int32_t* block_table, int table_stride, int nq, int nkv, int d, int page_size, int window, float scale,
     int num_pages, int32_t* status, const float* dist_bias, int dist_len, const float* head_gate, long long gate_stride,
-    int gate_off, float out_scale, long long out_stride, int out_off, uintptr_t stream);
+    int gate_off, float out_scale, long long out_stride, int out_off, int keep_first, int has_sink, float sink_score,
+    uintptr_t stream);
 
 // q, out: bfloat16 [T, nq*d]; cache: bfloat16 [pages, 2, nkv, page_size, d];
 // tiles: int32 [n_tiles][2] = (entry, first query row of the tile inside the entry), each tile
@@ -311,21 +321,25 @@ extern "C" int llm_paged_attention_prefill(
     int num_pages, int32_t* status, uintptr_t stream) {
     return llm_paged_attention_prefill_ex(q, out, cache, tiles, n_tiles, entry_slot, entry_q_start, entry_q_len, entry_kv_len,
                                           block_table, table_stride, nq, nkv, d, page_size, window, scale, num_pages, status,
-                                          nullptr, 0, nullptr, 0, 0, 1.0f, static_cast<long long>(nq) * d, 0, stream);
+                                          nullptr, 0, nullptr, 0, 0, 1.0f, static_cast<long long>(nq) * d, 0, 0, 0, 0.0f, stream);
 }
 
 // The same with what other attention layers add: `dist_bias` float32 [nq, dist_len], a learned bias by distance in
 // the exp2 domain (the table times log2 e), row min(i - j, dist_len - 1) of a head added to the scaled score of
 // query i and key j (dist_len == -1: `dist_bias` is float32 [nq, 3] = a temperature on the scaled score and the two
 // numbers of the bias r1 * ln(1 + r2 * (i - j)) that is taken off it, per head); `head_gate` float32, one value per (token, head) at [token * gate_stride + gate_off + head],
-// whose sigmoid multiplies the head's output; `out_scale`; the output row as a column range of a wider buffer.
+// whose sigmoid multiplies the head's output; `out_scale`; the output row as a column range of a wider buffer;
+// `keep_first`: with a window, the sequence's first so many keys stay visible to every later query; `has_sink`: one
+// more term exp(sink_score) in the softmax's denominator that carries no value.
 extern "C" int llm_paged_attention_prefill_ex(
     const void* q, void* out, const void* cache, const int32_t* tiles, int n_tiles, const int32_t* entry_slot,
     const int32_t* entry_q_start, const int32_t* entry_q_len, const int32_t* entry_kv_len,
     const int32_t* block_table, int table_stride, int nq, int nkv, int d, int page_size, int window, float scale,
     int num_pages, int32_t* status, const float* dist_bias, int dist_len, const float* head_gate, long long gate_stride,
-    int gate_off, float out_scale, long long out_stride, int out_off, uintptr_t stream) {
+    int gate_off, float out_scale, long long out_stride, int out_off, int keep_first, int has_sink, float sink_score,
+    uintptr_t stream) {
     if (n_tiles <= 0) return LLM_OK;
+    if (keep_first < 0) return LLM_REFUSED_SIZE;
     if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || page_size <= 0 || !llm_paged_prefill_supported(d)) return LLM_REFUSED_SIZE;
     if (dist_bias && dist_len <= 0 && dist_len != -1) return LLM_REFUSED_SIZE;
     if (!aligned16(q) || !aligned16(out) || !aligned16(cache) || out_stride % 2 || out_off % 2) return LLM_REFUSED_ALIGN;
@@ -333,7 +347,8 @@ extern "C" int llm_paged_attention_prefill_ex(
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     dim3 grid(nq, n_tiles);
     const float scale_log2e = scale * 1.4426950408889634f;
-    const bool ext = dist_bias || head_gate || out_scale != 1.0f || out_off != 0 || out_stride != static_cast<long long>(nq) * d;
+    const bool ext = dist_bias || head_gate || out_scale != 1.0f || out_off != 0 || out_stride != static_cast<long long>(nq) * d ||
+                     (keep_first > 0 && window > 0) || has_sink;
 #define LAUNCH(DD)                                                                                             \
     {                                                                                                          \
         auto kern = ext ? paged_prefill_attention_kernel<DD, true> : paged_prefill_attention_kernel<DD, false>;    \
@@ -344,7 +359,8 @@ extern "C" int llm_paged_attention_prefill_ex(
                                             static_cast<const bf16*>(cache), tiles, entry_slot, entry_q_start, \
                                             entry_q_len, entry_kv_len, block_table, table_stride, nq, nkv,     \
                                             page_size, window, scale_log2e, num_pages, status, dist_bias,      \
-                                            dist_len, head_gate, gate_stride, gate_off, out_scale, out_stride, out_off); \
+                                            dist_len, head_gate, gate_stride, gate_off, out_scale, out_stride, out_off, \
+                                            keep_first, has_sink, sink_score * 1.4426950408889634f); \
     }
     if (d == 64) LAUNCH(64) else LAUNCH(128)
 #undef LAUNCH

@@ -1152,10 +1152,15 @@ def paged_attention_decode(q: torch.Tensor, out: torch.Tensor, cache: torch.Tens
                            n_rows: int, positions, token_entry, entry_slot, block_table: torch.Tensor, nq: int,
                            nkv: int, d: int, page_size: int, window: Optional[int], scale: float, num_splits: int,
                            status: torch.Tensor, dist_bias_t: Optional[torch.Tensor] = None,
-                           analytic_bias: bool = False) -> torch.Tensor:
+                           analytic_bias: bool = False, keep_first: int = 0, sink: Optional[float] = None) -> torch.Tensor:
     """Attention for single decoded tokens (rows of q named by `rows`, or rows 0..n_rows-1), written
     into the same rows of `out`.  bfloat16 only.  `dist_bias_t` float32 [nq, distances]: a bias by distance TIMES
-    log2(e); row min(p - j, distances - 1) of a head joins the scaled score of the query at p and key j."""
+    log2(e); row min(p - j, distances - 1) of a head joins the scaled score of the query at p and key j.
+    `keep_first`: with a window, the sequence's first so many keys stay visible (one more split walks them, beside
+    the `num_splits` of the window).  `sink`: a score whose exponential joins the softmax's denominator without a value."""
+    keep_first = int(keep_first) if window else 0
+    if keep_first:
+        num_splits += 1
     _dev(q, out, cache, rows, positions, token_entry, entry_slot, block_table, status, dist_bias_t)
     if dist_bias_t is not None and (dist_bias_t.dtype != torch.float32 or dist_bias_t.dim() != 2 or dist_bias_t.shape[0] != nq):
         raise KernelError("dist_bias_t must be float32 [heads, distances]")
@@ -1169,13 +1174,15 @@ def paged_attention_decode(q: torch.Tensor, out: torch.Tensor, cache: torch.Tens
     need = _fn("attention_decode", "llm_paged_decode_scratch_floats", [c_int, c_int, c_int, c_int],
                restype=c_longlong)(n_rows, nq, d, num_splits)
     scratch = decode_scratch(q.device, int(need))
-    f = _fn("attention_decode", "llm_paged_attention_decode_biased",
+    f = _fn("attention_decode", "llm_paged_attention_decode_ex",
             [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
-             c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p])
+             c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float,
+             c_void_p])
     _check(f(_ptr(q), _ptr(out), _ptr(cache), _ptr(rows), n_rows, _ptr(positions), _ptr(token_entry),
              _ptr(entry_slot), _ptr(block_table), block_table.shape[1], nq, nkv, d, page_size,
              int(window) if window else 0, float(scale), cache.shape[0], num_splits, _ptr(scratch), _ptr(status),
-             _ptr(dist_bias_t), dist_len, _stream()), "paged_attention_decode")
+             _ptr(dist_bias_t), dist_len, keep_first, 0 if sink is None else 1, float(sink or 0.0), _stream()),
+           "paged_attention_decode")
     if num_splits > 1:
         global launch_count
         launch_count += 1                         # the merge kernel
@@ -1215,8 +1222,10 @@ def paged_attention_prefill_biased(q: torch.Tensor, out: torch.Tensor, out_off: 
                                    block_table: torch.Tensor, nq: int, nkv: int, d: int, page_size: int,
                                    window: Optional[int], scale: float, status: torch.Tensor,
                                    dist_bias_t: Optional[torch.Tensor] = None, head_gate: Optional[torch.Tensor] = None,
-                                   gate_off: int = 0, out_scale: float = 1.0, analytic_bias: bool = False) -> torch.Tensor:
-    """`analytic_bias`: `dist_bias_t` is float32 [nq, 3], per head a temperature on the scaled score and the numbers
+                                   gate_off: int = 0, out_scale: float = 1.0, analytic_bias: bool = False,
+                                   keep_first: int = 0, sink: Optional[float] = None) -> torch.Tensor:
+    """`keep_first`: with a window, the sequence's first so many keys stay visible to every later query.  `sink`: a score
+    whose exponential joins the softmax's denominator without a value.  `analytic_bias`: `dist_bias_t` is float32 [nq, 3], per head a temperature on the scaled score and the numbers
     r1, r2 of the bias r1 * ln(1 + r2 * (i - j)) that is taken off it (evaluated in the kernel; no table).
     `paged_attention_prefill` with what other attention layers add: `dist_bias_t` float32 [nq, distances], a bias by
     distance TIMES log2(e) (row min(i - j, distances - 1) of the head joins the scaled score); `head_gate` float32
@@ -1237,12 +1246,13 @@ def paged_attention_prefill_biased(q: torch.Tensor, out: torch.Tensor, out_off: 
     f = _fn("attention_prefill", "llm_paged_attention_prefill_ex",
             [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
              c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_int,
-             c_float, c_longlong, c_int, c_void_p])
+             c_float, c_longlong, c_int, c_int, c_int, c_float, c_void_p])
     _check(f(_ptr(q), _ptr(out), _ptr(cache), _ptr(tiles), n_tiles, _ptr(entry_slot), _ptr(entry_q_start),
              _ptr(entry_q_len), _ptr(entry_kv_len), _ptr(block_table), block_table.shape[1], nq, nkv, d,
              page_size, int(window) if window else 0, float(scale), cache.shape[0], _ptr(status), _ptr(dist_bias_t),
              dist_len, _ptr(head_gate),
              head_gate.stride(0) if head_gate is not None else 0, gate_off, float(out_scale), out.stride(0), out_off,
+             int(keep_first) if window else 0, 0 if sink is None else 1, float(sink or 0.0),
              _stream()), "paged_attention_prefill_biased")
     return out
 

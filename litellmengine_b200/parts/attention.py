@@ -295,7 +295,7 @@ class GatedAttentionMixer(BranchMixer):
         # mma.sync one, which adds the bias to its scores and gates as it stores), single tokens the general one
         if scored and spec.distance_bias is not None:
             raise ValueError("a distance table and a logarithmic distance bias or head temperature exclude one another")
-        self._tuned_prompt = (not self._tuned and not walked and compute_dtype == torch.bfloat16 and self.dv == self.d
+        self._tuned_prompt = (not self._tuned and compute_dtype == torch.bfloat16 and self.dv == self.d
                               and self.device.type == "cuda" and (self.gate_per_head or not spec.output_gate)
                               and ops.prefill_attention_supported(self.d))
         self._tuned_decode = self._tuned_prompt and ops.fast_attention_supported(self.d, self.nq // self.nkv)
@@ -421,7 +421,8 @@ class GatedAttentionMixer(BranchMixer):
                     q, out, out_col0, ctx.cache, work.padded_tiles if padded else work.prefill_tiles, n_tiles, b.entry_slot,
                     b.entry_q_start, b.entry_q_len, b.entry_kv_len, ctx.block_table, self.nq, self.nkv, self.d, ctx.page_size,
                     s.window, self.scale, ctx.status, dist_bias_t=self.dist_table_t, head_gate=gate,
-                    gate_off=col0 + self.g_off, out_scale=out_scale, analytic_bias=self.analytic)
+                    gate_off=col0 + self.g_off, out_scale=out_scale, analytic_bias=self.analytic,
+                    keep_first=self.keep_first, sink=self.sink)
             if not n_dec:
                 return
             rows = work.padded_rows if padded else (None if n_dec == b.num_tokens else work.decode_rows)
@@ -433,7 +434,8 @@ class GatedAttentionMixer(BranchMixer):
                 splits = decode_key_splits(q.device, n_dec, self.nkv, self._decode_reach(b))
                 ops.paged_attention_decode(q, a, ctx.cache, rows, n_dec, b.positions, b.token_entry, b.entry_slot,
                                            ctx.block_table, self.nq, self.nkv, self.d, ctx.page_size, s.window, self.scale, splits,
-                                           ctx.status, dist_bias_t=self.dist_table_t, analytic_bias=self.analytic)
+                                           ctx.status, dist_bias_t=self.dist_table_t, analytic_bias=self.analytic,
+                                           keep_first=self.keep_first, sink=self.sink)
                 if not direct:
                     ops.gate_mul(a, gate, col0 + self.g_off, out, out_col0, s.output_gate, out_scale,
                                  per_head=self.dv if self.gate_per_head else 0)

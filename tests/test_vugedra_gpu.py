@@ -480,3 +480,59 @@ def test_routed_feed_forward_every_way_it_runs(dtype, T):
     part.load({k: (v.to(tdt) if v.dim() == 2 and k != "router" else v.float()).to(DEV) for k, v in w.items()})
     got = _ops().as_tensor(part.forward(x.to(tdt).to(DEV)))
     assert (got.double().cpu() - ref).abs().max() < (3e-5 if dtype == "float32" else 0.05) * max(1.0, float(ref.abs().max()))
+
+
+@pytest.mark.parametrize("d,group,window,keep", [(64, 2, 100, 5), (128, 1, 64, 70), (128, 2, 140, 6), (128, 4, 257, 129), (128, 8, None, 0),
+                                                 (64, 4, 30, 0)])
+def test_tensor_core_attention_with_kept_keys_and_sink(d, group, window, keep):
+    """The kernels that a 16-bit run takes at head sizes 64 and 128: a prompt portion that starts in the middle of a page
+    with keys before it (row tiles of 128 whose window begins several key tiles after the kept keys), and single tokens in
+    the split-key decode kernel, where one more split walks the kept keys.  Keys that would win by far sit among the kept
+    ones, just behind them, and at the window's first and just before it."""
+    ops = _ops()
+    N, past, page, G, scale = 420, 37, 16, 2, 0.2
+    H, T = G * group, N - past
+    g = torch.Generator().manual_seed(d + group)
+    q, k, v = (torch.randn(N, n, d, generator=g, dtype=F64) for n in (H, G, G))
+    w = window or N
+    for i, j in ((419, max(keep - 1, 0)), (418, keep), (417, 417 - w + 1), (416, 416 - w), (300, 3), (299, max(299 - w, 0))):
+        k[j] = q[i, ::group] * (40.0 / d)          # a score of about ten
+    q[N - 2] = -q[N - 2].abs() * 3                  # a query that looks away from all it sees: the sink takes its weight
+    k[max(N - 2 - w + 1, 0):N - 1] = k[max(N - 2 - w + 1, 0):N - 1].abs()
+    k[:keep] = k[:keep].abs()
+    q, k, v = (t.to(torch.bfloat16).double() for t in (q, k, v))
+    mask = {"size": window, "keep_first": keep} if window else None
+    vis = pv.visible_keys(N, mask)[past:]
+    kh, vh = (t.permute(1, 0, 2).repeat_interleave(group, 0) for t in (k, v))
+    scores = (q[past:].permute(1, 0, 2) @ kh.transpose(1, 2)) * scale
+    ref = pv.softmax_core(scores, vh, vis, sink=True).permute(1, 0, 2)
+    assert ref[N - 2 - past].abs().max() < 0.2 * ref.abs().max()        # the sink took nearly all of that query's weight
+    order = np.random.RandomState(2).permutation(N // page + 6)[:-(-N // page)]
+    block_table = torch.full((3, len(order) + 2), -1, dtype=torch.int32)
+    block_table[1, :len(order)] = torch.as_tensor(order, dtype=torch.int32)
+    block_table = block_table.to(DEV)
+    cache = torch.zeros(N // page + 6, 2, G, page, d, dtype=torch.bfloat16, device=DEV)
+    for j in range(N):
+        cache[order[j // page], 0, :, j % page] = k[j].to(torch.bfloat16).to(DEV)
+        cache[order[j // page], 1, :, j % page] = v[j].to(torch.bfloat16).to(DEV)
+    qd = q[past:].reshape(T, -1).to(torch.bfloat16).to(DEV)
+    out = torch.zeros(T, H * d, dtype=torch.bfloat16, device=DEV)
+    status = torch.zeros(2, dtype=torch.int32, device=DEV)
+    tiles = _i32([(0, r0) for r0 in range(0, T, ops.PREFILL_TILE_ROWS)])
+    ops.paged_attention_prefill_biased(qd, out, 0, cache, tiles, tiles.shape[0], _i32([1]), _i32([0]), _i32([T]), _i32([N]),
+                                       block_table, H, G, d, page, window, scale, status, keep_first=keep, sink=0.0)
+    assert status.tolist() == [0, 0]
+    assert (out.double().cpu().view(T, H, d) - ref).abs().max() < 0.06
+    assert ops.fast_attention_supported(d, group)
+    for splits in (1, 3):
+        a = torch.zeros(T, H * d, dtype=torch.bfloat16, device=DEV)
+        picked = [T - 1, T - 2, T - 3, T - 4, 5, 263, 262]
+        ops.paged_attention_decode(qd, a, cache, _i32(picked + [-1]), len(picked) + 1, _i32(list(range(past, N))), _i32([0] * T),
+                                   _i32([1]), block_table, H, G, d, page, window, scale, splits, status, keep_first=keep, sink=0.0)
+        assert status.tolist() == [0, 0]
+        assert (a.double().cpu().view(T, H, d)[picked] - ref[picked]).abs().max() < 0.06, splits
+    # the edges matter: without the kept keys, or with ordinary softmax, the result is another
+    if window and keep:
+        other = pv.softmax_core(scores, vh, pv.visible_keys(N, {"size": window})[past:], sink=True).permute(1, 0, 2)
+        assert (other - ref).abs().max() > 0.05
+    assert (pv.softmax_core(scores, vh, vis, sink=False).permute(1, 0, 2) - ref).abs().max() > 0.1
