@@ -2,7 +2,7 @@
 """Benchmark of the engine on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers L]
-                    [--impl ours|reference] [--points LIST | --no-points] [--design tobovik|gubidra|komazen [--sizes LIST]]
+                    [--impl ours|reference] [--points LIST | --no-points] [--design tobovik|gubidra|komazen|vugedra [--sizes LIST]]
 
 Headline (`value`): decode tokens/s of `batch` requests whose context ends at 4,096 tokens, on a
 model with the layer sizes of Qwen3-8B (36 layers unless --layers says fewer; the JSON names both
@@ -21,7 +21,7 @@ the Qwen3-32B shape at batch 16 (each sub-record names its sizes).
 prefill and decode of the Tobovik design beside Qwen3 at equal width, heads, feed-forward, depth and
 vocabulary, and the design's own kernels beside the like kernels of the Qwen3 path with their roofline
 fractions.  `--design gubidra` does the same for the Gubidra design beside Tobovik, its closest model, and
-`--design komazen` for the Komazen design beside Qwen3.
+`--design komazen` for the Komazen design beside Qwen3, `--design vugedra` for the Vugedra design beside Gubidra.
 Without it the workload and the line above are what they always were.
 
 `--impl reference` times the unmodified reference engine (float32, its only precision) on the same
@@ -586,6 +586,169 @@ def komazen_dict(width, ff, heads, kv, layers):
             "layers": [att if i % 2 == 0 else lat(i - 2 if i % 4 == 3 else None) for i in range(layers)]}
 
 
+def vugedra_dict(width, ff, heads, kv, layers):
+    """Attention (a window of 1,024 keys that keeps the first four, neighbouring pairs of half a head rotated with stretched
+    frequencies, a sink, a gate per head), gated linear attention, latent attention over one cached row of 576 per token,
+    gated linear attention, and so on; heads of 128.  Every layer has eight experts of half the feed-forward size of which
+    two of ten router outputs are chosen (two of the ten are no experts), and a shared expert of a quarter."""
+    mlp = {"kind": "moe", "expert": {"ff": ff // 2}, "router": {"experts": 8, "identity": 2, "top": 2}, "shared": {"ff": ff // 4}}
+    att = {"type": "attention", "mlp": mlp, "mixer": {
+        "heads": heads, "kv_heads": kv, "dim": DESIGN_HEAD, "vdim": DESIGN_HEAD, "scale": DESIGN_HEAD ** -0.5,
+        "mask": {"size": 1024, "keep_first": 4},
+        "rot": {"base": 10000.0, "dims": DESIGN_HEAD // 2, "scaling": {"factor": 4.0, "original": 1024, "fast": 32.0, "slow": 1.0}}}}
+    gla = {"type": "gla", "mlp": mlp,
+           "mixer": {"heads": max(1, heads // 2), "dim": DESIGN_HEAD, "vdim": DESIGN_HEAD, "tau": 8.0, "rank": 64}}
+    lat = {"type": "latent_attention", "mlp": mlp, "mixer": {
+        "heads": heads, "dim": DESIGN_HEAD, "rot_dim": 64, "vdim": DESIGN_HEAD, "q_rank": 3 * width // 8, "kv_rank": 512,
+        "scale": (DESIGN_HEAD + 64) ** -0.5,
+        "rot": {"base": 10000.0, "dims": 64, "scaling": {"factor": 4.0, "original": 1024, "fast": 32.0, "slow": 1.0}}}}
+    return {"architecture": "Vugedra", "vocab": DESIGN_VOCAB, "width": width, "norm": {"eps": 1e-5},
+            "layers": [(att, gla, lat, gla)[i % 4] for i in range(layers)]}
+
+
+def vugedra_bench(args, pk, measure) -> int:
+    """`--design vugedra`: the design beside Gubidra (the closest model: recurrent layers beside windowed attention, routed
+    experts in every layer) at equal width, heads, expert sizes, depth and vocabulary, and its kernels beside their like."""
+    import math
+    import torch
+    import types
+    from litellmengine_b200.config import config_from_dict
+    from litellmengine_b200.config.specs import PositionSpec
+    from litellmengine_b200.csrc import ops
+    from litellmengine_b200.csrc.microbench import Flusher, timed
+    from litellmengine_b200.parts.registry import lookup
+    dev = "cuda:0"
+    sizes = {}
+    for name, (width, ff, heads, kv, layers) in DESIGN_SIZES.items():
+        if args.sizes and name not in args.sizes.split(","):
+            continue
+        sizes[name] = {"shape": {"width": width, "ff": ff, "heads": heads, "kv_heads": kv, "layers": layers, "vocab": DESIGN_VOCAB}}
+        for label, cfg in (("vugedra", vugedra_dict(width, ff, heads, kv, layers)), ("gubidra", gubidra_dict(width, ff, heads, kv, layers))):
+            sizes[name][label] = measure(config_from_dict(cfg))
+            gc.collect()
+            torch.cuda.empty_cache()
+        v, g = sizes[name]["vugedra"], sizes[name]["gubidra"]
+        sizes[name]["vugedra_over_gubidra"] = {k: round(v[k] / g[k], 3) for k in v if k.endswith("tok_s")}
+    flush = Flusher(dev)
+    width, ff, heads, kv, _ = DESIGN_SIZES["w4096"]
+    T, hbm, d = 2048, pk["hbm_gbs"] * 1e9, DESIGN_HEAD
+    tensor_peak = pk.get("bf16_tflops", 1590.0) * 1e12
+    kernels = {}
+
+    def add(name, fn, nbytes=None, flops=None):
+        sec = timed(fn, 5, 3, flush)
+        rec = {"us": round(sec * 1e6, 2)}
+        if nbytes is not None:
+            rec.update(gbs=round(nbytes / sec / 1e9, 1), frac_of_hbm=round(nbytes / sec / hbm, 4))
+        if flops is not None:
+            rec.update(tflops=round(flops / sec / 1e12, 2), frac_of_bf16_peak=round(flops / sec / tensor_peak, 4))
+        kernels[name] = rec
+
+    i32 = lambda x: torch.as_tensor(x, dtype=torch.int32, device=dev)
+    pos = torch.arange(T, device=dev, dtype=torch.int32)
+    prompt = types.SimpleNamespace(positions=pos, token_entry=i32([0] * T), entry_slot=i32([0]), entry_q_start=i32([0]),
+                                   entry_q_len=i32([T]))
+    status = torch.zeros(2, dtype=torch.int32, device=dev)
+    # the norm around the residual add
+    h, y, w = torch.randn(T, width, device=dev), torch.randn(T, width, device=dev), torch.ones(width, device=dev)
+    one = torch.ones(1, device=dev)
+    tri = (one, w, w * 0.1)
+    add("tanh_norm (new: norm of a sublayer's output + residual add + norm of the next input, bfloat16 copy)",
+        lambda: ops.tanh_norm(h, y, tri, tri, torch.bfloat16), nbytes=T * width * (4 + 4 + 4 + 2))
+    add("rmsnorm (like: residual add + norm, bfloat16 copy)", lambda: ops.rmsnorm(h, w, 1e-5, torch.bfloat16, delta=y, write_sum=True),
+        nbytes=T * width * (4 + 4 + 4 + 2))
+    # between the projection and attention: biases, norm over the projection, pair rotation, page write
+    pages = T // PAGE
+    qkv = torch.randn(T, (heads + 2 * kv) * d + heads, device=dev)
+    cache = torch.zeros(pages, 2, kv, PAGE, d, device=dev, dtype=torch.bfloat16)
+    tbl = torch.arange(pages, device=dev, dtype=torch.int32).view(1, pages)
+    scaling = (4.0, 1024.0, 32.0, 1.0)
+    rot = lookup("position", "rope_pairs")(PositionSpec("rope_pairs", 1e4, d // 2, (("scaling", scaling), ("magnitude", 0.1 * math.log(4.0) + 1.0))),
+                                           d, dev).kernel_args()
+    bq, bk = torch.zeros(heads * d, device=dev), torch.zeros(kv * d, device=dev)
+    wq, wk = torch.ones(heads * d, device=dev), torch.ones(kv * d, device=dev)
+    prep = lambda r: ops.attention_prepare(qkv, 0, heads * d, (heads + kv) * d, (bq, bk, bk), wq, wk, "projection", 1e-5, None,
+                                           cache[:, 0], cache[:, 1], pos, prompt.token_entry, prompt.entry_slot, tbl, heads, kv, d, d,
+                                           PAGE, status, torch.bfloat16, rotation=r)
+    prep_bytes = T * (heads + 2 * kv) * d * (4 + 2)
+    add("attention_prepare with the rotation of pairs (new)", lambda: prep(rot), nbytes=prep_bytes)
+    add("attention_prepare without a rotation (like: what Tobovik's attention takes)", lambda: prep(None), nbytes=prep_bytes)
+    # prompt attention: window 1,024, four kept keys, a sink, a gate per head
+    cache.normal_()
+    qa = torch.randn(T, heads * d, device=dev).to(torch.bfloat16)
+    oa = torch.empty_like(qa)
+    tiles = torch.tensor([(0, r0) for r0 in range(0, T, ops.PREFILL_TILE_ROWS)][::-1], device=dev, dtype=torch.int32)
+    e_len = i32([T])
+    window = 1024
+    walked = sum(min(p + 1, window) for p in range(T))
+    attn_flops = 4.0 * heads * d * walked
+    common = (cache, tiles, tiles.shape[0], prompt.entry_slot, prompt.entry_q_start, e_len, e_len, tbl, heads, kv, d, PAGE, window,
+              d ** -0.5, status)
+    add("prompt attention, window 1024 with kept keys, sink and a gate per head (new; mma.sync): 2048 tokens",
+        lambda: ops.paged_attention_prefill_biased(qa, oa, 0, *common, head_gate=qkv, gate_off=(heads + 2 * kv) * d, keep_first=4, sink=0.0),
+        flops=attn_flops)
+    add("prompt attention, the same kernel with the window and the gate alone (like: what Gubidra's prompt portions take)",
+        lambda: ops.paged_attention_prefill_biased(qa, oa, 0, *common, head_gate=qkv, gate_off=(heads + 2 * kv) * d), flops=attn_flops)
+    Bd, ctx = 64, 2048
+    dpages = ctx // PAGE
+    dcache = torch.randn(Bd * dpages, 2, kv, PAGE, d, device=dev).to(torch.bfloat16)
+    dtbl = torch.arange(Bd * dpages, device=dev, dtype=torch.int32).view(Bd, dpages)
+    dpos = torch.full((Bd,), ctx - 1, device=dev, dtype=torch.int32)
+    dent = torch.arange(Bd, device=dev, dtype=torch.int32)
+    kv_bytes = Bd * window * 2 * kv * d * 2
+    add(f"decode attention, split-key kernel with kept keys and sink (new): {Bd} tokens at position {ctx - 1}, window {window}",
+        lambda: ops.paged_attention_decode(qa[:Bd], oa[:Bd], dcache, None, Bd, dpos, dent, dent, dtbl, heads, kv, d, PAGE, window, d ** -0.5,
+                                           2, status, keep_first=4, sink=0.0), nbytes=kv_bytes)
+    add("decode attention, split-key kernel with the window alone (like)",
+        lambda: ops.paged_attention_decode(qa[:Bd], oa[:Bd], dcache, None, Bd, dpos, dent, dent, dtbl, heads, kv, d, PAGE, window, d ** -0.5,
+                                           2, status), nbytes=kv_bytes)
+    ogen = torch.empty(Bd, heads * d, device=dev, dtype=torch.bfloat16)
+    add("decode attention, the general kernel with kept keys and sink (new: the 32-bit mode and odd shapes)",
+        lambda: ops.paged_attention_generic_kv(qa[:Bd], dcache[:, 0], dcache[:, 1], dpos, dent, dent, dtbl, heads, kv, d, d, PAGE, window,
+                                               d ** -0.5, status, ogen, keep_first=4, sink=0.0), nbytes=kv_bytes)
+    # the latent layer's small kernels with the rotation of pairs beside the half-split one
+    Q, R, P = 3 * width // 8, 512, 64
+    proj = torch.randn(T, Q + R + P, device=dev)
+    rows = torch.zeros(pages, 1, PAGE, R + P, device=dev, dtype=torch.bfloat16)
+    invf, rd, mag, _ = lookup("position", "rope_pairs")(PositionSpec("rope_pairs", 1e4, P, (("scaling", scaling), ("magnitude", 1.14))), P, dev).kernel_args()
+    ones_q, ones_r = torch.ones(Q, device=dev), torch.ones(R, device=dev)
+    for label, pairs in (("pairs, stretched (new)", True), ("half-split (like)", False)):
+        add(f"latent_prepare, rotation of {label}",
+            lambda pairs=pairs: ops.latent_prepare(proj, 0, Q, Q, R, P, P, ones_q, ones_r, 1e-5, invf, rows, prompt, tbl, PAGE, status,
+                                                   torch.bfloat16, rot_pairs=pairs, rot_mag=mag if pairs else 1.0),
+            nbytes=T * (Q + R + P) * (4 + 2))
+    q32 = torch.randn(T, heads * (d + P), device=dev)
+    for label, pairs in (("pairs, stretched (new)", True), ("half-split (like)", False)):
+        add(f"latent_q_split, rotation of {label}",
+            lambda pairs=pairs: ops.latent_q_split(q32, pos, invf, heads, d, P, R, P, torch.bfloat16, rot_pairs=pairs, rot_mag=mag if pairs else 1.0),
+            nbytes=T * heads * (d + P) * (4 + 2))
+    # the router and what joins the experts' sum
+    E, top, fe = 8, 2, ff // 2
+    x = torch.randn(T, width, device=dev).to(torch.bfloat16)
+    wr = torch.randn(E + 2, width, device=dev) * width ** -0.5
+    corr = torch.randn(E + 2, device=dev) * 0.1
+    add("moe_route, softmax with a correction and two outputs that are no experts (new)",
+        lambda: ops.moe_route(x, wr, top, None, 1.0, score="softmax", correction=corr, identity=2), nbytes=T * (width * 2 + E * 4))
+    add("moe_route, sigmoid with groups (like)", lambda: ops.moe_route(x, wr[:E].contiguous(), top, (4, 2), 1.0), nbytes=T * (width * 2 + E * 4))
+    gu = torch.randn(T, E * 2 * fe, device=dev)
+    dense = ops.moe_route(x, wr[:E].contiguous(), top, (4, 2), 1.0)
+    add("moe_act, plain silu gate (new)", lambda: ops.moe_act(gu, dense, E, fe, float("inf"), 1.0, torch.bfloat16, shift=0.0),
+        nbytes=T * (top * 2 * fe * 4 + E * fe * 2))
+    add("moe_act, clamped gate (like)", lambda: ops.moe_act(gu, dense, E, fe, 7.0, 1.702, torch.bfloat16),
+        nbytes=T * (top * 2 * fe * 4 + E * fe * 2))
+    out32, sh = torch.randn(T, width, device=dev), torch.randn(T, width, device=dev)
+    idw = torch.rand(T, device=dev)
+    add("moe_finish (new: the token's own share and the shared expert join the experts' sum)",
+        lambda: ops.moe_finish(out32, x, idw, sh), nbytes=T * width * (4 + 4 + 4 + 2))
+    add("residual_add (like)", lambda: ops.residual_add(out32, sh), nbytes=T * width * 12)
+    print(json.dumps({"metric": "tokens/s of the Vugedra design beside Gubidra at equal sizes (bfloat16, random weights)",
+                      "design": "vugedra", "prompt_tokens": 2048, "decode_context": 1024, "steps": args.steps,
+                      "warmup": args.warmup, "sizes": sizes, "kernels_at_w4096": kernels,
+                      "peaks": {"hbm_gbs": pk["hbm_gbs"], "bf16_tflops": round(tensor_peak / 1e12, 1), "source": pk["source"]},
+                      "l2": "kernel timings: a 256 MB buffer is overwritten between launches; steps read every weight"}))
+    return 0
+
+
 def komazen_bench(args, pk, measure) -> int:
     """`--design komazen`: the design beside Qwen3 (the closest model: softmax attention and a dense gated feed-forward
     in every layer) at equal width, heads, feed-forward, depth and vocabulary, and its kernels beside their like."""
@@ -975,6 +1138,8 @@ def design_bench(args, pk) -> int:
         return gubidra_bench(args, pk, measure)
     if args.design == "komazen":
         return komazen_bench(args, pk, measure)
+    if args.design == "vugedra":
+        return vugedra_bench(args, pk, measure)
     sizes = {}
     for name, (width, ff, heads, kv, layers) in DESIGN_SIZES.items():
         if args.sizes and name not in args.sizes.split(","):
@@ -1094,9 +1259,9 @@ def main() -> int:
     ap.add_argument("--points", default=",".join(ALL_POINTS),
                     help="which extra measurements to take: " + ",".join(ALL_POINTS))
     ap.add_argument("--no-points", action="store_true", help="the headline, prefill and e2e only")
-    ap.add_argument("--design", choices=["tobovik", "gubidra", "komazen"],
+    ap.add_argument("--design", choices=["tobovik", "gubidra", "komazen", "vugedra"],
                     help="instead of the default workload: this design beside its closest model (tobovik and komazen beside "
-                         "Qwen3, gubidra beside tobovik) at equal sizes, and its kernels")
+                         "Qwen3, gubidra beside tobovik, vugedra beside gubidra) at equal sizes, and its kernels")
     ap.add_argument("--sizes", default="", help="with --design: which of " + ",".join(DESIGN_SIZES) + " (default: all)")
     args = ap.parse_args()
 
