@@ -114,6 +114,8 @@ class TanhNorm:
         if isinstance(delta, PendingNormed):
             post = delta.norm.triple() if delta.norm is not None else None
             delta = delta.y
+        if isinstance(delta, ops.PartialSum) and delta.rounds_to is not None:
+            delta = ops.as_tensor(delta)             # k-splits of a product that is not 32-bit: their sum is rounded first
         return ops.tanh_norm(x, delta, post, self.triple(), out_dtype, rows=rows)
 
     def add_normed(self, h: torch.Tensor, y) -> None:
