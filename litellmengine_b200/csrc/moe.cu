@@ -27,13 +27,12 @@
 
 #define MOE_ROUTE_THREADS 256
 #define MOE_ROUTE_TOKENS 4        // tokens a block takes: the router's matrix is read once for all of them
-#define MOE_ROUTE_SPAN 1024       // entries of a row that one warp takes at a time when the rows are few
 
 template <typename TX>
 __global__ void moe_route_kernel(const TX* __restrict__ x, const float* __restrict__ wr, float* __restrict__ dense,
                                  int32_t* __restrict__ ids, float* __restrict__ weights, int num_tokens, int W, int E,
                                  int top, int groups, int keep, float route_scale, int vec, int softmax,
-                                 const float* __restrict__ correction, int identity, float* __restrict__ idw, int chunks, int span) {
+                                 const float* __restrict__ correction, int identity, float* __restrict__ idw) {
     pdl_begin();
     extern __shared__ float smem[];
     const int G = groups > 0 ? groups : 1;
@@ -55,22 +54,14 @@ __global__ void moe_route_kernel(const TX* __restrict__ x, const float* __restri
         for (int i = tid; i < nt * W; i += blockDim.x) xs[i] = to_f32(x[t0 * W + i]);
     }
     __syncthreads();
-    // A warp takes an item = (output e, span c of its row) and leaves the span's dot products with the block's tokens;
-    // the spans of a row are added up in order afterwards.  With few outputs a row is cut into spans of
-    // `span` entries (about MOE_ROUTE_SPAN; `chunks` > 1), so that every warp has work and a lane keeps eight loads in flight: a step
-    // of a few tokens is one or two blocks, and a warp that walked a whole row alone was bound by the latency of its
-    // loads (34 us for 8 tokens and 10 outputs of 4,096; a prompt's many blocks hide it).
-    float* part = reinterpret_cast<float*>(allowed + MOE_ROUTE_TOKENS * E);            // [TOKENS][E][chunks]
-    for (int item = warp; item < E * chunks; item += MOE_ROUTE_THREADS / 32) {
-        const int e = item / chunks, c = item - e * chunks;
-        const int lo = c * span, hi = min(W, lo + span);
+    for (int e = warp; e < E; e += MOE_ROUTE_THREADS / 32) {       // a warp an expert: its row against the block's tokens
         const float* w = wr + static_cast<size_t>(e) * W;
         float dot[MOE_ROUTE_TOKENS];
 #pragma unroll
         for (int k = 0; k < MOE_ROUTE_TOKENS; ++k) dot[k] = 0.0f;
-        if (vec) {                                      // sixteen bytes of the row a lane and trip, eight trips in flight
-#pragma unroll 8
-            for (int i = lo + lane * 4; i < hi; i += 128) {
+        if (vec) {                                      // sixteen bytes of the row a lane and trip, four trips in flight
+#pragma unroll 4
+            for (int i = lane * 4; i < W; i += 128) {
                 const float4 wv = *reinterpret_cast<const float4*>(w + i);
 #pragma unroll
                 for (int k = 0; k < MOE_ROUTE_TOKENS; ++k) {      // rows past nt hold stale data: never used
@@ -79,7 +70,7 @@ __global__ void moe_route_kernel(const TX* __restrict__ x, const float* __restri
                 }
             }
         } else {
-            for (int i = lo + lane; i < hi; i += 32) {
+            for (int i = lane; i < W; i += 32) {
                 const float wv = w[i];
 #pragma unroll
                 for (int k = 0; k < MOE_ROUTE_TOKENS; ++k) dot[k] += wv * xs[k * W + i];
@@ -88,14 +79,8 @@ __global__ void moe_route_kernel(const TX* __restrict__ x, const float* __restri
 #pragma unroll
         for (int k = 0; k < MOE_ROUTE_TOKENS; ++k) {
             const float d = warp_sum(dot[k]);
-            if (lane == 0 && k < nt) part[(k * E + e) * chunks + c] = d;
+            if (lane == 0 && k < nt) score[k * E + e] = softmax ? d : 1.0f / (1.0f + expf(-d));
         }
-    }
-    __syncthreads();
-    for (int idx = tid; idx < nt * E; idx += blockDim.x) {
-        float d = 0.0f;
-        for (int c = 0; c < chunks; ++c) d += part[idx * chunks + c];
-        score[idx] = softmax ? d : 1.0f / (1.0f + expf(-d));
     }
     __syncthreads();
     if (softmax) {                                   // a warp a token: maximum, exponentials, their sum
@@ -183,14 +168,11 @@ extern "C" int llm_moe_route(const void* x, int x_dtype, const float* wr, float*
     if (identity < 0 || identity >= E || (identity > 0 && !idw)) return LLM_REFUSED_SIZE;
     if (W <= 0 || E <= 0 || top <= 0 || top > E || top > 64 || groups < 0) return LLM_REFUSED_SIZE;
     if (groups > 0 && (E % groups || keep <= 0 || keep > groups || keep * (E / groups) < top)) return LLM_REFUSED_SIZE;
-    const int vec = W % 8 == 0 && aligned16(x) && aligned16(wr);
-    const int chunks = (vec && E < 32 && W > MOE_ROUTE_SPAN) ? min((W + MOE_ROUTE_SPAN - 1) / MOE_ROUTE_SPAN, 16) : 1;
-    const int span = chunks > 1 ? ((W + chunks - 1) / chunks + 127) / 128 * 128 : W;      // whole trips of a warp
-    const size_t smem = MOE_ROUTE_TOKENS * (static_cast<size_t>(W) + 2 * E + (groups > 0 ? groups : 1) +
-                                            static_cast<size_t>(E) * chunks) * sizeof(float);
+    const size_t smem = MOE_ROUTE_TOKENS * (static_cast<size_t>(W) + 2 * E + (groups > 0 ? groups : 1)) * sizeof(float);
     if (smem > 200 * 1024) return LLM_REFUSED_SIZE;
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     const dim3 grid((num_tokens + MOE_ROUTE_TOKENS - 1) / MOE_ROUTE_TOKENS);
+    const int vec = W % 8 == 0 && aligned16(x) && aligned16(wr);
 #define LAUNCH(TX)                                                                                                  \
     do {                                                                                                            \
         auto kern = moe_route_kernel<TX>;                                                                           \
@@ -200,7 +182,7 @@ extern "C" int llm_moe_route(const void* x, int x_dtype, const float* wr, float*
             if (e != cudaSuccess) return static_cast<int>(e);                                                       \
         }                                                                                                           \
         launch_pdl(kern, grid, dim3(MOE_ROUTE_THREADS), smem, s, static_cast<const TX*>(x), wr, dense, ids, weights,  \
-                   num_tokens, W, E, top, groups, keep, route_scale, vec, softmax, correction, identity, idw, chunks, span); \
+                   num_tokens, W, E, top, groups, keep, route_scale, vec, softmax, correction, identity, idw);      \
     } while (0)
     if (x_dtype == LLM_DT_F32) LAUNCH(float);
     else if (x_dtype == LLM_DT_BF16) LAUNCH(bf16);
