@@ -536,3 +536,59 @@ def test_tensor_core_attention_with_kept_keys_and_sink(d, group, window, keep):
         other = pv.softmax_core(scores, vh, pv.visible_keys(N, {"size": window})[past:], sink=True).permute(1, 0, 2)
         assert (other - ref).abs().max() > 0.05
     assert (pv.softmax_core(scores, vh, vis, sink=False).permute(1, 0, 2) - ref).abs().max() > 0.1
+
+
+@pytest.mark.parametrize("H,D,V,tau", [(2, 8, 16, 1.0), (3, 16, 8, 4.0), (1, 48, 64, 16.0), (2, 128, 128, 8.0), (5, 4, 6, 32.0)])
+def test_gated_linear_attention_in_one_pass_in_portions_and_token_by_token(H, D, V, tau):
+    """The recurrent mixer's kernels on projections made from given weights, against the plain token-by-token function:
+    the decays from the low-rank projection (a channel whose bias keeps it from ever decaying carries an impulse from the
+    first token to the last; one whose bias makes it forget at once loses it), the recurrence in one pass, in portions
+    that carry the state in the request's slot (down to two tokens and one), and through the kernel of decode steps,
+    which makes the decays itself; the state left behind is checked too."""
+    ops = _ops()
+    T, Wd, rank, eps = 203, 24, 5, 1e-5
+    g = torch.Generator().manual_seed(H * 100 + D)
+    u = torch.randn(T, Wd, generator=g, dtype=F64)
+    w = {"q": torch.randn(H * D, Wd, generator=g, dtype=F64) * Wd ** -0.5, "k": torch.randn(H * D, Wd, generator=g, dtype=F64) * Wd ** -0.5,
+         "v": torch.randn(H * V, Wd, generator=g, dtype=F64) * Wd ** -0.5, "g": torch.randn(H * V, Wd, generator=g, dtype=F64) * Wd ** -0.5,
+         "a1": torch.randn(rank, Wd, generator=g, dtype=F64) * Wd ** -0.5, "a2": torch.randn(H * D, rank, generator=g, dtype=F64),
+         "a2.b": torch.randn(H * D, generator=g, dtype=F64) * 2, "norm": 1 + 0.1 * torch.randn(V, generator=g, dtype=F64),
+         "o": torch.eye(H * V, dtype=F64)}
+    w["a2"][0], w["a2.b"][0] = 0.0, 60.0          # never decays
+    w["a2"][1], w["a2.b"][1] = 0.0, -60.0 * tau   # forgets at once
+    u[0] *= 4.0                                   # an impulse at the first token
+    m = {"heads": H, "dim": D, "vdim": V, "tau": tau}
+    ref, s_ref = pv.gla(u, w, "", m, eps)
+    cols = [u @ w[n].T for n in ("q", "k", "v", "g", "a1")]
+    proj = torch.cat(cols, dim=1).float()
+    offs = (0, H * D, 2 * H * D, 2 * H * D + H * V)
+    a_off = 2 * H * D + 2 * H * V
+    w2t, b2, nw = _f32(w["a2"].t()), _f32(w["a2.b"]), _f32(w["norm"])
+    slots = _i32([2])
+
+    def run(cuts, step=False):
+        state = torch.zeros((4, H, D, V), dtype=torch.float32, device=DEV)
+        state[1] = 7.0                                            # another request's state stays untouched
+        out = torch.zeros((T, H * V), dtype=torch.float32, device=DEV)
+        pd = proj.to(DEV)
+        at = 0
+        for n in cuts:
+            rows = pd[at:at + n].contiguous()
+            if step and n == 1:
+                ops.gla_step(rows, offs, None, nw, eps, D ** -0.5, 1.0, out[at:at + n], 0, state, slots, _i32([0]), 1, H, D, V,
+                             decay=(a_off, rank, w2t, b2, tau))
+            else:
+                alpha = ops.gla_decay(rows, a_off, rank, w2t, b2, tau)
+                ops.gla_scan(rows, offs, alpha, nw, eps, D ** -0.5, 1.0, out[at:at + n], 0, state, slots, _i32([0]), _i32([n]), None, 1,
+                             ops.GLA_FULL, None, None, H, D, V)
+            at += n
+        assert at == T and float((state[1] - 7.0).abs().max()) == 0 and float(state[0].abs().max()) == 0
+        return out.double().cpu(), state[2].double().cpu()
+
+    scale = max(1.0, float(ref.abs().max()))
+    for what, (got, s) in (("one pass", run([T])), ("portions", run([2, 1, 16, 17, 2, 64, 70, 31])),
+                           ("a portion, then the decode kernel token by token", run([33] + [1] * (T - 33), step=True))):
+        assert (got - ref).abs().max() < 3e-5 * scale, what
+        assert (s - s_ref).abs().max() < 3e-5 * max(1.0, float(s_ref.abs().max())), what
+    flat = s_ref.reshape(H * D, V)
+    assert flat[0].abs().max() > 10 * flat[1].abs().max()        # the impulse is kept by one channel and forgotten by the other
